@@ -1,0 +1,90 @@
+// Shared host/device helpers for the dgq_* entry points.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "dgq.h"
+
+#define DGQ_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define DGQ_REQUIRE(cond, code) \
+  do {                          \
+    if (!(cond)) return (code); \
+  } while (0)
+
+static inline cudaStream_t dgq_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+static inline int32_t dgq_launch_status() {
+  return cudaGetLastError() == cudaSuccess ? DGQ_OK : DGQ_ERR_LAUNCH;
+}
+
+static inline bool dgq_aligned(const void* p, uintptr_t a) {
+  return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
+}
+
+static inline int64_t dgq_cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Number of SMs of the current device (148 on B200); cached per process.
+static inline int dgq_sm_count() {
+  static int cached = 0;
+  if (cached == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      cached = n;
+    else
+      return 148;
+  }
+  return cached;
+}
+
+// Grid for a grid-stride kernel: enough CTAs to fill the machine a few times
+// over, rounded to a multiple of the SM count, never more than the work needs.
+static inline unsigned dgq_grid(int64_t work_items, int threads, int ctas_per_sm = 8) {
+  int64_t need = dgq_cdiv(work_items, threads);
+  int64_t cap = (int64_t)dgq_sm_count() * ctas_per_sm;
+  if (need < 1) need = 1;
+  return (unsigned)(need < cap ? need : cap);
+}
+
+// ---- the scalar formulas of the path --------------------------------------
+// q = clamp(round(w/scale + zero), 0, maxq) with true division and round-half-even.
+__device__ __forceinline__ float dgq_quant_level(float w, float scale, float zero, float maxq) {
+  float q = rintf(__fadd_rn(__fdiv_rn(w, scale), zero));
+  return fminf(fmaxf(q, 0.f), maxq);
+}
+__device__ __forceinline__ float dgq_dequant_level(float q, float scale, float zero) {
+  return __fmul_rn(__fsub_rn(q, zero), scale);
+}
+// scale = (max-min)/maxq (1 if zero), zero = round(-min/scale)
+__device__ __forceinline__ void dgq_scale_zero(float mn, float mx, float maxq, float& scale,
+                                               float& zero) {
+  float s = __fdiv_rn(__fsub_rn(mx, mn), maxq);
+  if (s == 0.f) s = 1.f;
+  scale = s;
+  zero = rintf(__fdiv_rn(-mn, s));
+}
+
+template <typename T>
+__device__ __forceinline__ float dgq_to_float(T v);
+template <>
+__device__ __forceinline__ float dgq_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float dgq_to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float dgq_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T>
+__device__ __forceinline__ T dgq_from_float(float v);
+template <>
+__device__ __forceinline__ float dgq_from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half dgq_from_float<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 dgq_from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}

@@ -1,0 +1,253 @@
+// Blockwise GPTQ quantization of one weight matrix given the inverse-Hessian factor.
+//
+// For every block of `blocksize` (<= 128) columns:
+//   1. gptq_block_kernel - one warp per weight row.  Lane l keeps columns l, l+32,
+//      l+64, l+96 of the block in registers; the block of U sits in shared memory.
+//      Columns are visited in order: the owning lane's value is broadcast with a
+//      shuffle, every lane evaluates the quantize/dequantize formulas on it (so the
+//      scaled error needs no second broadcast) and applies the error feedback to the
+//      columns it holds.  Codes, dequantized values and the scaled errors leave
+//      through coalesced stores.
+//   2. trailing update - W[:, i2:] -= Err * U[i1:i2, i2:]  (fp32 matrix product).
+//
+// Group scale/zero are taken from W as it stands when the group's first column is
+// reached by the block loop (all earlier blocks' trailing updates applied, none of
+// the current block's in-block updates), which for groups that start inside a block
+// means the values the block had at entry.
+#include "common.cuh"
+#include "sgemm_view.cuh"
+
+namespace {
+
+constexpr int MAX_BLOCK = 128;
+constexpr int ROWS_PER_CTA = 16;  // one warp each
+
+struct QuantArgs {
+  float* W; int64_t ldw;
+  const float* U; int64_t ldu;
+  uint8_t* codes; int64_t ldc;
+  float* scales; float* zeros; int n_groups;
+  float* err;            // (N_out, MAX_BLOCK)
+  double* total_error;
+  int N_out, K, i1, bw;  // block start and width
+  int group;             // effective group size (K for per-channel)
+  float maxq;
+};
+
+__global__ void __launch_bounds__(ROWS_PER_CTA * 32)
+gptq_block_kernel(const QuantArgs a) {
+  extern __shared__ float Us[];  // bw x MAX_BLOCK, row j = U[i1 + j][i1 .. i1 + bw)
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int idx = threadIdx.x; idx < a.bw * MAX_BLOCK; idx += blockDim.x) {
+    int j = idx / MAX_BLOCK, c = idx % MAX_BLOCK;
+    Us[idx] = (c < a.bw && c >= j) ? a.U[(int64_t)(a.i1 + j) * a.ldu + a.i1 + c] : 0.f;
+  }
+  __syncthreads();
+
+  double err_sq = 0.0;
+  for (int row = blockIdx.x * ROWS_PER_CTA + warp; row < a.N_out; row += gridDim.x * ROWS_PER_CTA) {
+    float* wrow = a.W + (int64_t)row * a.ldw + a.i1;
+    float w[4], s_c[4], z_c[4], what[4], ev[4];
+    uint32_t code[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      int c = t * 32 + lane;
+      w[t] = (c < a.bw) ? wrow[c] : 0.f;
+      what[t] = 0.f; ev[t] = 0.f; code[t] = 0;
+    }
+    // ---- scale / zero of every column this lane holds
+    if (a.group >= a.bw) {
+      // the group spans this whole block (and possibly more): one pair for the row
+      const int g = a.i1 / a.group;
+      float s, z;
+      if (a.i1 % a.group == 0) {
+        // the group starts here: min/max over W[row][i1 .. i1+group)
+        float mn = INFINITY, mx = -INFINITY;
+        const int gend = min(a.group, a.K - a.i1);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          int c = t * 32 + lane;
+          if (c < a.bw) { mn = fminf(mn, w[t]); mx = fmaxf(mx, w[t]); }
+        }
+        for (int c = a.bw + lane; c < gend; c += 32) {
+          float v = wrow[c];
+          mn = fminf(mn, v); mx = fmaxf(mx, v);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        dgq_scale_zero(mn, mx, a.maxq, s, z);
+        if (lane == 0) {
+          a.scales[(int64_t)row * a.n_groups + g] = s;
+          a.zeros[(int64_t)row * a.n_groups + g] = z;
+        }
+      } else {
+        s = a.scales[(int64_t)row * a.n_groups + g];
+        z = a.zeros[(int64_t)row * a.n_groups + g];
+      }
+#pragma unroll
+      for (int t = 0; t < 4; ++t) { s_c[t] = s; z_c[t] = z; }
+    } else {
+      // groups start inside the block, at multiples of `group` (i1 is one too)
+      const int g0 = a.i1 / a.group;
+      if (a.group >= 32) {
+        // a group covers group/32 whole register slots
+        const int slots = a.group / 32;
+#pragma unroll
+        for (int t0 = 0; t0 < 4; t0 += 1) {
+          if (t0 % slots != 0) continue;
+          float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            if (t >= t0 && t < t0 + slots) {
+              int c = t * 32 + lane;
+              if (c < a.bw) { mn = fminf(mn, w[t]); mx = fmaxf(mx, w[t]); }
+            }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          }
+          float s, z;
+          dgq_scale_zero(mn, mx, a.maxq, s, z);
+          const int gi = g0 + (t0 * 32) / a.group;
+          if (lane == 0 && t0 * 32 < a.bw) {
+            a.scales[(int64_t)row * a.n_groups + gi] = s;
+            a.zeros[(int64_t)row * a.n_groups + gi] = z;
+          }
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            if (t >= t0 && t < t0 + slots) { s_c[t] = s; z_c[t] = z; }
+        }
+      } else {
+        // several groups per slot: segmented reduction over `group` adjacent lanes
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          int c = t * 32 + lane;
+          float mn = (c < a.bw) ? w[t] : INFINITY, mx = (c < a.bw) ? w[t] : -INFINITY;
+          for (int o = a.group >> 1; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          }
+          float s, z;
+          dgq_scale_zero(mn, mx, a.maxq, s, z);
+          s_c[t] = s; z_c[t] = z;
+          if (c < a.bw && (lane % a.group) == 0) {
+            a.scales[(int64_t)row * a.n_groups + g0 + c / a.group] = s;
+            a.zeros[(int64_t)row * a.n_groups + g0 + c / a.group] = z;
+          }
+        }
+      }
+    }
+    // ---- the column loop
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      if (t * 32 >= a.bw) break;
+      const int jn = min(32, a.bw - t * 32);
+      for (int jl = 0; jl < jn; ++jl) {
+        const int j = t * 32 + jl;
+        const float wj = __shfl_sync(0xffffffffu, w[t], jl);
+        const float sj = __shfl_sync(0xffffffffu, s_c[t], jl);
+        const float zj = __shfl_sync(0xffffffffu, z_c[t], jl);
+        const float* urow = Us + j * MAX_BLOCK;
+        const float q = dgq_quant_level(wj, sj, zj, a.maxq);
+        const float wh = dgq_dequant_level(q, sj, zj);
+        const float e = __fdiv_rn(__fsub_rn(wj, wh), urow[j]);
+        if (lane == jl) {
+          code[t] = (uint32_t)q;
+          what[t] = wh;
+          ev[t] = e;
+        }
+        // error feedback on the columns to the right (separate multiply and subtract,
+        // the order of operations of an outer-product update)
+        if (lane > jl) w[t] = __fsub_rn(w[t], __fmul_rn(e, urow[t * 32 + lane]));
+#pragma unroll
+        for (int u = t + 1; u < 4; ++u) w[u] = __fsub_rn(w[u], __fmul_rn(e, urow[u * 32 + lane]));
+      }
+    }
+    // ---- outputs
+    float* erow = a.err + (int64_t)row * MAX_BLOCK;
+    uint8_t* crow = a.codes + (int64_t)row * a.ldc + a.i1;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      int c = t * 32 + lane;
+      if (c < a.bw) {
+        wrow[c] = what[t];
+        crow[c] = (uint8_t)code[t];
+        erow[c] = ev[t];
+        err_sq += (double)ev[t] * (double)ev[t];
+      } else {
+        erow[c] = 0.f;
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) err_sq += __shfl_xor_sync(0xffffffffu, err_sq, o);
+  if (lane == 0 && err_sq != 0.0) atomicAdd(a.total_error, err_sq);
+}
+
+bool valid_bits(int b) { return b == 2 || b == 3 || b == 4 || b == 8; }
+
+}  // namespace
+
+DGQ_EXPORT int64_t dgq_gptq_quantize_workspace_bytes(int32_t N_out, int32_t K, int32_t blocksize) {
+  if (N_out <= 0 || K <= 0 || blocksize <= 0 || blocksize > MAX_BLOCK) return DGQ_ERR_ARG;
+  return (int64_t)N_out * MAX_BLOCK * (int64_t)sizeof(float);
+}
+
+DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int64_t ldu,
+                                     int32_t N_out, int32_t K, int32_t bits, int32_t group_size,
+                                     int32_t blocksize, uint8_t* codes, int64_t ldc, float* scales,
+                                     float* zeros, double* total_error, void* ws, int64_t ws_bytes,
+                                     void* stream) {
+  DGQ_REQUIRE(W && U && codes && scales && zeros && total_error && ws, DGQ_ERR_ARG);
+  DGQ_REQUIRE(N_out > 0 && K > 0 && ldw >= K && ldu >= K && ldc >= K && valid_bits(bits), DGQ_ERR_ARG);
+  DGQ_REQUIRE(blocksize > 0 && blocksize <= MAX_BLOCK, DGQ_ERR_UNSUPPORTED);
+  const bool per_channel = group_size <= 0 || group_size >= K;
+  const int group = per_channel ? K : group_size;
+  if (!per_channel) {
+    const bool divides = blocksize % group == 0 && (group >= 32 ? group % 32 == 0
+                                                                 : (group & (group - 1)) == 0);
+    const bool multiple = group % blocksize == 0;
+    DGQ_REQUIRE(divides || multiple, DGQ_ERR_UNSUPPORTED);
+  }
+  DGQ_REQUIRE(ws_bytes >= dgq_gptq_quantize_workspace_bytes(N_out, K, blocksize), DGQ_ERR_WORKSPACE);
+  DGQ_REQUIRE(dgq_aligned(ws, 16), DGQ_ERR_ALIGN);
+  cudaStream_t st = dgq_stream(stream);
+
+  static bool attr_set = false;
+  const size_t smem = (size_t)MAX_BLOCK * MAX_BLOCK * sizeof(float);
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gptq_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return DGQ_ERR_LAUNCH;
+    attr_set = true;
+  }
+  if (cudaMemsetAsync(total_error, 0, sizeof(double), st) != cudaSuccess) return DGQ_ERR_LAUNCH;
+
+  QuantArgs a;
+  a.W = W; a.ldw = ldw; a.U = U; a.ldu = ldu; a.codes = codes; a.ldc = ldc;
+  a.scales = scales; a.zeros = zeros;
+  a.n_groups = per_channel ? 1 : (int)dgq_cdiv(K, group);
+  a.err = reinterpret_cast<float*>(ws);
+  a.total_error = total_error;
+  a.N_out = N_out; a.K = K; a.group = group; a.maxq = (float)((1 << bits) - 1);
+  const unsigned grid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, ROWS_PER_CTA),
+                                                    (int64_t)dgq_sm_count() * 2);
+  for (int i1 = 0; i1 < K; i1 += blocksize) {
+    a.i1 = i1;
+    a.bw = std::min(blocksize, K - i1);
+    gptq_block_kernel<<<grid, ROWS_PER_CTA * 32, (size_t)a.bw * MAX_BLOCK * sizeof(float), st>>>(a);
+    const int i2 = i1 + a.bw;
+    if (i2 < K) {
+      GemmArgs g{a.err, MAX_BLOCK, 1, U + (int64_t)i1 * ldu + i2, ldu, 1,
+                 W + i2, ldw, 1, N_out, K - i2, a.bw, -1.f, 1.f};
+      launch_gemm<0>(g, st);
+    }
+  }
+  return dgq_launch_status();
+}

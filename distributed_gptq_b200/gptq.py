@@ -1,0 +1,256 @@
+"""Layer-level GPTQ: the ``GPTQ`` and ``Quantizer`` classes.
+
+Mirrors ``src/distributed_gptq/core/gptq.py`` of the reference (constructor
+arguments, ``add_batch`` / ``quantize`` / ``pack_weights``, the ``H`` / ``nsamples`` /
+``scale`` / ``zero`` / ``maxq`` attributes and the keys of the returned stats), with
+every computation done by the sm_100a kernels behind ``libdgq.so``.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _C
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class Quantizer:
+    """Scale/zero search and round-to-nearest on their own.
+
+    ``find_params`` evaluates ``scale = (max-min)/maxq``, ``zero = round(-min/scale)``
+    per row (reference ``core/gptq.py:165-169``); ``quantize`` evaluates
+    ``clamp(round(x/scale + zero), 0, maxq)`` and returns the dequantized values
+    ``(q - zero)*scale`` (``core/gptq.py:175,179``).  The integer levels of the last
+    call are kept in ``codes``.
+    """
+
+    def __init__(self, bits: int = 4):
+        self.configure(bits)
+        self.scale: Optional[torch.Tensor] = None
+        self.zero: Optional[torch.Tensor] = None
+        self.codes: Optional[torch.Tensor] = None
+
+    def configure(self, bits: int, **_unused) -> None:
+        if bits not in (2, 3, 4, 8):
+            raise ValueError(f"bits must be 2, 3, 4 or 8, got {bits}")
+        self.bits = bits
+        self.maxq = 2 ** bits - 1
+
+    def find_params(self, x: torch.Tensor, weight: bool = True) -> None:
+        x2 = x.reshape(x.shape[0], -1) if weight else x.reshape(1, -1)
+        self.scale, self.zero = _C.find_params(x2.float().contiguous(), self.bits)
+
+    def quantize(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.ready():
+            raise RuntimeError("call find_params first")
+        x2 = x.reshape(self.scale.numel(), -1).float().contiguous()
+        self.codes, xh = _C.quantize_rows(x2, self.scale, self.zero, self.bits)
+        self.codes = self.codes.reshape(x.shape)
+        return xh.reshape(x.shape).to(x.dtype)
+
+    def ready(self) -> bool:
+        return self.scale is not None
+
+
+class GPTQ:
+    """GPTQ of one ``nn.Linear`` / ``nn.Conv2d`` (reference ``core/gptq.py:16-266``).
+
+    ``H`` holds the raw sum ``Σ XᵀX`` in fp32 like the reference's attribute;
+    normalisation, damping, act-order and the inverse factor are applied to a copy
+    inside :meth:`quantize`.
+    """
+
+    def __init__(self, layer: nn.Module, bits: int = 4, group_size: int = 128,
+                 actorder: bool = False, percdamp: float = 0.01, blocksize: int = 128,
+                 device: Optional[torch.device] = None):
+        self.layer = layer
+        self.bits = bits
+        self.group_size = group_size
+        self.actorder = actorder
+        self.percdamp = percdamp
+        self.blocksize = blocksize
+        if device is None:
+            device = layer.weight.device if layer.weight.is_cuda else torch.device("cuda")
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("distributed_gptq_b200 has no CPU path: GPTQ needs a CUDA device")
+        self.maxq = 2 ** bits - 1
+        self.scale: Optional[torch.Tensor] = None
+        self.zero: Optional[torch.Tensor] = None
+        self.codes: Optional[torch.Tensor] = None
+        self.g_idx: Optional[torch.Tensor] = None
+        self.perm: Optional[torch.Tensor] = None
+        self._Hbuf: Optional[torch.Tensor] = None
+        self.nsamples = 0
+        self.columns = self._weight_matrix().shape[1]
+        self._info = None
+
+    # ------------------------------------------------------------------ helpers
+    def _weight_matrix(self) -> torch.Tensor:
+        W = self.layer.weight.data
+        if isinstance(self.layer, nn.Conv2d):
+            W = W.flatten(1)
+        return W
+
+    @property
+    def H(self) -> Optional[torch.Tensor]:
+        if self._Hbuf is None:
+            return None
+        return self._Hbuf[:self.columns, :self.columns]
+
+    @H.setter
+    def H(self, value: Optional[torch.Tensor]) -> None:
+        if value is None:
+            self._Hbuf = None
+            return
+        K = self.columns
+        assert value.shape == (K, K)
+        K8 = _round_up(K, 8)
+        buf = torch.zeros((K8, K8), dtype=torch.float32, device=self.device)
+        buf[:K, :K] = value.to(self.device, torch.float32)
+        self._Hbuf = buf
+
+    def _tokens(self, inp: torch.Tensor) -> torch.Tensor:
+        """Flattens a batch to ``(tokens, columns)`` the way the layer consumes it."""
+        if isinstance(self.layer, nn.Conv2d):
+            unfold = nn.Unfold(self.layer.kernel_size, dilation=self.layer.dilation,
+                               padding=self.layer.padding, stride=self.layer.stride)
+            x = unfold(inp)                      # (b, C*kh*kw, L)
+            return x.permute(0, 2, 1).reshape(-1, x.shape[1])
+        return inp.reshape(-1, inp.shape[-1])
+
+    # ------------------------------------------------------------------ Hessian
+    def add_batch(self, inp: torch.Tensor, out: Optional[torch.Tensor] = None) -> None:
+        """``H += XᵀX``; ``nsamples += batch`` (reference ``core/gptq.py:63-89``).
+
+        A 2-D input counts as one sample.  ``out`` is accepted and ignored, as in the
+        reference.  Activations are taken in bf16 (fp32/fp16 inputs are rounded to
+        bf16 first) and accumulated in fp32 on the tensor cores.
+        """
+        if inp.dim() == 2 and not isinstance(self.layer, nn.Conv2d):
+            inp = inp.unsqueeze(0)
+        batch = inp.shape[0]
+        x = self._tokens(inp.to(self.device))
+        K = self.columns
+        assert x.shape[1] == K, f"expected {K} input features, got {x.shape[1]}"
+        K8 = _round_up(K, 8)
+        if self._Hbuf is None:
+            self._Hbuf = torch.zeros((K8, K8), dtype=torch.float32, device=self.device)
+            self._info = _C.new_info(self.device)
+        if K8 != K:
+            xp = torch.zeros((x.shape[0], K8), dtype=x.dtype, device=self.device)
+            xp[:, :K] = x
+            x = xp
+        xb = _C.to_bf16(x)
+        self.nsamples += batch
+        if xb.shape[0] > 0:
+            _C.hessian_accum(xb, self._Hbuf, 1.0, 0, self._info)
+
+    # ------------------------------------------------------------------ quantize
+    def quantize(self) -> Dict[str, Any]:
+        """Blockwise GPTQ of the layer's weight (reference ``core/gptq.py:91-214``).
+
+        Writes the dequantized weights back into ``layer.weight`` in its dtype and
+        keeps ``codes`` (uint8, ``(out, in)``), ``scale`` / ``zero`` (fp32,
+        ``(out, n_groups)``) and ``g_idx`` (int32 group of every input column) on the
+        object.  Returns the reference's stats keys plus timings-free extras.
+        """
+        if self._Hbuf is None or self.nsamples == 0:
+            raise RuntimeError("no calibration data: call add_batch before quantize")
+        if self._info is not None:
+            _C.raise_on_info(self._info, "hessian accumulation")
+        Wm = self._weight_matrix()
+        N_out, K = Wm.shape
+        W = Wm.to(self.device, torch.float32).contiguous().clone()
+        H = self.H
+        scale = float(torch.tensor(2.0 / self.nsamples, dtype=torch.float32))
+
+        perm = invperm = None
+        if self.actorder:
+            perm, invperm = _C.actorder_perm(H, scale)
+        Hp, dead = _C.hessian_prepare(H, scale, self.percdamp, perm)
+        Wp = _C.permute_cols(W, perm, dead)
+        info = _C.new_info(self.device)
+        U = _C.inv_chol_upper(Hp, info)
+        codes, scales, zeros, terr = _C.gptq_quantize(Wp, U, self.bits, self.group_size,
+                                                      self.blocksize)
+        g = K if (self.group_size <= 0 or self.group_size >= K) else self.group_size
+        if self.actorder:
+            Q = _C.permute_cols(Wp, invperm)
+            codes = _C.permute_cols(codes, invperm)
+            g_idx = (invperm // g).to(torch.int32)
+        else:
+            Q = Wp
+            g_idx = (torch.arange(K, device=self.device, dtype=torch.int32) // g)
+        _C.raise_on_info(info, "damped inverse")
+
+        self.codes, self.scale, self.zero, self.g_idx, self.perm = codes, scales, zeros, g_idx, perm
+        self.layer.weight.data = Q.reshape(self.layer.weight.shape).to(
+            device=self.layer.weight.device, dtype=self.layer.weight.dtype)
+        total_error = float(terr.item())
+        return {
+            "bits": self.bits,
+            "group_size": self.group_size,
+            "total_error": total_error,
+            "compression_ratio": 32.0 / self.bits,
+            "scale_shape": self.scale.shape,
+            "zero_shape": self.zero.shape,
+        }
+
+    def fasterquant(self, blocksize: Optional[int] = None, percdamp: Optional[float] = None,
+                    group_size: Optional[int] = None, groupsize: Optional[int] = None,
+                    actorder: Optional[bool] = None) -> Dict[str, Any]:
+        """Same work as :meth:`quantize`; arguments override the constructor's values."""
+        if blocksize is not None:
+            self.blocksize = blocksize
+        if percdamp is not None:
+            self.percdamp = percdamp
+        if group_size is None:
+            group_size = groupsize
+        if group_size is not None:
+            self.group_size = group_size
+        if actorder is not None:
+            self.actorder = actorder
+        return self.quantize()
+
+    # ------------------------------------------------------------------ packing
+    def pack_weights(self, format: int = _C.FMT_BYTES_HI_FIRST) -> Dict[str, Any]:
+        """Packed codes and parameters (reference ``core/gptq.py:216-266``).
+
+        The default format is the reference's byte packing of this method (first
+        code in the high bits); pass ``_C.FMT_BYTES_LO_FIRST`` for the
+        ``QuantizedLinear`` layout or ``_C.FMT_INT32_LE`` for 32-bit words.
+        """
+        if self.codes is None:
+            raise RuntimeError("call quantize before pack_weights")
+        return {
+            "packed_weights": _C.pack(self.codes, self.bits, format),
+            "scale": self.scale,
+            "zero": self.zero,
+            "g_idx": self.g_idx,
+            "bits": self.bits,
+            "group_size": self.group_size,
+            "shape": self.codes.shape,
+        }
+
+    def free(self) -> None:
+        self._Hbuf = None
+        self._info = None
+        torch.cuda.empty_cache()
+
+
+def quantize_layer_gptq(layer: nn.Module, calibration_data, bits: int = 4, group_size: int = 128,
+                        **kwargs) -> Dict[str, Any]:
+    """One-call helper (reference ``core/gptq.py:383-417``): feeds every batch of
+    ``calibration_data`` to ``add_batch`` and quantizes."""
+    q = GPTQ(layer, bits=bits, group_size=group_size, **kwargs)
+    for batch in calibration_data:
+        inp = batch[0] if isinstance(batch, (tuple, list)) else batch
+        q.add_batch(inp, None)
+    return q.quantize()

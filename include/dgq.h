@@ -1,0 +1,217 @@
+/*
+ * dgq.h - C ABI of the B200 (sm_100a) GPTQ quantization path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes, is
+ * asynchronous on the CUDA stream it is given (a `cudaStream_t` passed as
+ * `void*`; NULL is the default stream) and returns a status: 0 = enqueued,
+ * negative = rejected on the host before any launch (see DGQ_ERR_*).
+ * The library never allocates or frees device memory: the caller owns every
+ * buffer, including the workspaces sized by the *_workspace_bytes functions.
+ * Conditions found on the device (a non-positive Cholesky pivot, a bounded wait
+ * that ran out) are written to the caller's `info` words, which the caller reads
+ * after synchronising.
+ *
+ * Each declaration names the reference interface it stands in for, as
+ * file:line inside the reference project (src/distributed_gptq/...).
+ *
+ * Matrices are row-major.  W is (N_out, K): rows are output features, columns
+ * are input features, so columns line up with the K x K Hessian.
+ */
+#ifndef DGQ_H_
+#define DGQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define DGQ_OK                 0
+#define DGQ_ERR_ARG          (-1)  /* null pointer, non-positive size, unknown enum */
+#define DGQ_ERR_ALIGN        (-2)  /* pointer or leading dimension not aligned as documented */
+#define DGQ_ERR_WORKSPACE    (-3)  /* workspace smaller than *_workspace_bytes() */
+#define DGQ_ERR_ARCH         (-4)  /* current device is not compute capability 10.x */
+#define DGQ_ERR_LAUNCH       (-5)  /* the CUDA runtime refused a launch or a set-up call */
+#define DGQ_ERR_UNSUPPORTED  (-6)  /* valid request outside what this build implements */
+#define DGQ_ERR_SIZE         (-7)  /* size beyond a documented maximum */
+
+/* device-side conditions, written to info[0] (info[1] holds a detail word) */
+#define DGQ_INFO_OK              0
+#define DGQ_INFO_NOT_POSDEF      1  /* info[1] = index of the first non-positive pivot */
+#define DGQ_INFO_WAIT_TIMEOUT    2  /* info[1] = which wait gave up */
+
+/* ---- enums -------------------------------------------------------------- */
+/* packing formats */
+#define DGQ_FMT_BYTES_HI_FIRST   1  /* GPTQ.pack_weights, core/gptq.py:229-257 */
+#define DGQ_FMT_BYTES_LO_FIRST   2  /* QuantizedLinear.pack_weights, models/layers.py:76-93 */
+#define DGQ_FMT_INT32_LE         3  /* pack_weights_kernel, kernels/triton_kernels.py:203-222 */
+/* element types of float buffers */
+#define DGQ_F32   0
+#define DGQ_F16   1
+#define DGQ_BF16  2
+
+const char* dgq_status_string(int32_t status);
+int32_t     dgq_version(void);
+/* 0 when the current device can run this library (compute capability 10.x). */
+int32_t     dgq_device_check(void);
+
+/* ---- Hessian accumulation ------------------------------------------------
+ * Replaces GPTQ.add_batch, core/gptq.py:63-89 (`self.H += inp @ inp.t()`).
+ *
+ * H(K,K) += alpha * X^T X with X (T,K) bf16 row-major, fp32 accumulation on the
+ * 5th-generation tensor cores (TMA -> shared memory -> tcgen05.mma -> TMEM).
+ * The full symmetric matrix is updated.  Requirements: X 16-byte aligned,
+ * ldx (elements) a multiple of 8, K >= 8, H 16-byte aligned, ldh a multiple of 4.
+ * `info` (device, 2 x int32, or NULL) receives DGQ_INFO_WAIT_TIMEOUT if a bounded
+ * wait inside the kernel ran out; it is never cleared by the library.
+ * `splits` >= 1 fixes the number of token ranges the work is cut into (each
+ * range adds into H with fp32 reductions, so splits > 1 is not bit-reproducible);
+ * 0 lets the library choose.
+ */
+int32_t dgq_hessian_accum(const void* X_bf16, int64_t T, int32_t K, int64_t ldx,
+                          float* H, int64_t ldh, float alpha, int32_t splits,
+                          int32_t* info, void* stream);
+
+/* fp32 -> bf16 (round to nearest even) for activations that arrive as fp32
+ * (core/gptq.py:88 upcasts; the tensor-core path takes bf16). n elements. */
+int32_t dgq_cast_f32_to_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);
+/* fp16 -> bf16 */
+int32_t dgq_cast_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, void* stream);
+
+/* ---- Hessian preparation --------------------------------------------------
+ * Replaces core/gptq.py:112-119 (normalise + damp) and adds what the reference
+ * stores but never applies (act-order, core/gptq.py:49) and dead-column handling.
+ *
+ * dgq_actorder_perm: perm = stable argsort, in descending order (ties keep
+ *   ascending index), of the prepared diagonal scale*H_ii with zero entries read
+ *   as 1; invperm[perm[i]] = i.
+ * dgq_hessian_prepare: Hout[i][j] = scale * H[p(i)][p(j)]  (p = perm, or identity
+ *   when perm is NULL); a zero diagonal entry becomes 1 and marks the column dead;
+ *   then diag += percdamp * mean(diag).  dead_out (K bytes, in permuted order)
+ *   receives the dead mask.  H and Hout must not overlap.  ws: K floats.
+ * dgq_permute_cols_f32: dst[r][i] = dead && dead[i] ? 0 : src[r][perm[i]]
+ * dgq_permute_cols_u8 : dst[r][i] = src[r][perm[i]]
+ */
+int32_t dgq_actorder_perm(const float* H, int32_t K, int64_t ldh, float scale,
+                          int32_t* perm, int32_t* invperm, void* stream);
+int64_t dgq_hessian_prepare_workspace_bytes(int32_t K);
+int32_t dgq_hessian_prepare(const float* H, int64_t ldh, float* Hout, int64_t ldo, int32_t K,
+                            float scale, float percdamp, const int32_t* perm,
+                            uint8_t* dead_out, void* ws, int64_t ws_bytes, void* stream);
+int32_t dgq_permute_cols_f32(const float* src, int64_t lds, float* dst, int64_t ldd,
+                             int32_t rows, int32_t cols, const int32_t* perm,
+                             const uint8_t* dead, void* stream);
+int32_t dgq_permute_cols_u8(const uint8_t* src, int64_t lds, uint8_t* dst, int64_t ldd,
+                            int32_t rows, int32_t cols, const int32_t* perm, void* stream);
+
+/* ---- damped inverse -------------------------------------------------------
+ * Replaces core/gptq.py:121-122 (`cholesky_inverse(linalg.cholesky(H))`) and the
+ * upper-Cholesky step of the GPTQ algorithm.
+ *
+ * In place: A (K,K) symmetric positive definite (only its lower triangle and
+ * diagonal are read) -> U upper triangular with A^-1 = U^T U; the strict lower
+ * triangle of the result is zero.  Blocked fp32 factorisation on the device.
+ * info (device, 2 x int32): DGQ_INFO_NOT_POSDEF and the pivot index on failure.
+ * lda a multiple of 4, A 16-byte aligned.
+ */
+int64_t dgq_inv_chol_workspace_bytes(int32_t K);
+int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t* info,
+                           void* ws, int64_t ws_bytes, void* stream);
+
+/* ---- blockwise quantization -----------------------------------------------
+ * Replaces the block/column loop of GPTQ.quantize, core/gptq.py:131-194, with the
+ * scale/zero formula of :165-169 and the quantize/dequantize formula of :175,179.
+ *
+ * W (N_out,K) fp32 in/out: on return it holds the dequantized weights Q.
+ * U (K,K): the factor from dgq_inv_chol_upper.  codes (N_out,K) uint8.
+ * scales/zeros (N_out, n_groups) fp32 with n_groups = ceil(K/group_size), or 1 when
+ * group_size <= 0 or >= K (per output channel).  total_error: one device double,
+ * receives sum(((w - w_hat)/d)^2) (core/gptq.py:183,191); it is overwritten.
+ * blocksize must be 128 or less and group_size, when it is smaller than K, must
+ * either divide blocksize or be a multiple of it.
+ */
+int64_t dgq_gptq_quantize_workspace_bytes(int32_t N_out, int32_t K, int32_t blocksize);
+int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int64_t ldu,
+                          int32_t N_out, int32_t K, int32_t bits, int32_t group_size,
+                          int32_t blocksize, uint8_t* codes, int64_t ldc,
+                          float* scales, float* zeros, double* total_error,
+                          void* ws, int64_t ws_bytes, void* stream);
+
+/* ---- scale/zero and quantize on their own ("Quantizer.find_params/quantize") --
+ * find_params: per row of x (rows, cols): scale = (max-min)/maxq (1 if zero),
+ *   zero = round(-min/scale)                       (core/gptq.py:165-169)
+ * quantize_rows: q = clamp(round(x/scale + zero), 0, maxq), x_hat = (q-zero)*scale
+ *   with one (scale, zero) per row; either output may be NULL. (core/gptq.py:175,179)
+ */
+int32_t dgq_find_params(const float* x, int64_t ldx, int32_t rows, int32_t cols, int32_t bits,
+                        float* scale, float* zero, void* stream);
+int32_t dgq_quantize_rows(const float* x, int64_t ldx, int32_t rows, int32_t cols, int32_t bits,
+                          const float* scale, const float* zero,
+                          uint8_t* q, int64_t ldq, float* x_hat, int64_t ldh, void* stream);
+
+/* ---- packing and dequantization -------------------------------------------
+ * dgq_pack replaces GPTQ.pack_weights (core/gptq.py:229-257, format 1),
+ * QuantizedLinear.pack_weights (models/layers.py:76-93, format 2) and
+ * pack_weights_kernel (kernels/triton_kernels.py:203-222, format 3).
+ * codes (rows, cols) uint8, contiguous.  Packed row length in bytes:
+ *   format 1: cols*bits/8 for 2- and 4-bit (cols must divide evenly), cols otherwise;
+ *   format 2: ceil(cols/2) for 4-bit, cols otherwise;
+ *   format 3: 4*ceil(cols / (32/bits)).
+ * dgq_packed_row_bytes returns that length (negative status on bad arguments).
+ * dgq_unpack is the inverse (QuantizedLinear.unpack_weights models/layers.py:105-120,
+ * GPTQDequantizer._unpack_4bit core/dequantizer.py:68-89).
+ * dgq_unpack_dequant fuses the inverse with (code - zero[r][g]) * scale[r][g]
+ * (models/layers.py:122-136, core/dequantizer.py:31-66, dequantize_kernel
+ * kernels/triton_kernels.py:82-123); g = g_idx[c] when g_idx is given, else
+ * c / group_size (one group when group_size <= 0 or >= cols).  scales/zeros are
+ * (rows, n_groups) of param_dtype (DGQ_F32 or DGQ_F16); out is (rows, cols) of
+ * out_dtype, contiguous.
+ */
+int64_t dgq_packed_row_bytes(int32_t cols, int32_t bits, int32_t format);
+int32_t dgq_pack(const uint8_t* codes, int32_t rows, int32_t cols, int32_t bits, int32_t format,
+                 void* packed, void* stream);
+int32_t dgq_unpack(const void* packed, int32_t rows, int32_t cols, int32_t bits, int32_t format,
+                   uint8_t* codes, void* stream);
+int32_t dgq_unpack_dequant(const void* packed, const void* scales, const void* zeros,
+                           const int32_t* g_idx, int32_t rows, int32_t cols, int32_t n_groups,
+                           int32_t bits, int32_t group_size, int32_t format,
+                           int32_t param_dtype, int32_t out_dtype, void* out, void* stream);
+
+/* ---- quantized linear -------------------------------------------------------
+ * Implements the operator QuantizedLinear.forward dispatches to,
+ * torch.ops.gptq.linear(x, qweight, scales, zeros, g_idx, bias)
+ * (models/layers.py:150-153), and stands in for quantized_matmul_kernel
+ * (kernels/triton_kernels.py:126-183).
+ *
+ * y(M,N_out) = x(M,K) * dequant(qweight)^T + bias, fp32 accumulation.
+ * qweight is in the QuantizedLinear layout (format 2: nibble pairs for 4-bit, one
+ * byte per code otherwise); scales/zeros (N_out, n_groups) fp16; g_idx (K) int32
+ * group of every input column, or NULL for c / group_size; bias (N_out) of
+ * bias_dtype or NULL; x and y of x_dtype (DGQ_F32, DGQ_F16 or DGQ_BF16).
+ * Tuned for M <= 16 (bound by the packed weights' HBM traffic); larger M runs
+ * in chunks of 16 rows.
+ */
+int32_t dgq_qlinear_forward(const void* x, int32_t x_dtype, int32_t M,
+                            const uint8_t* qweight, const void* scales_f16, const void* zeros_f16,
+                            const int32_t* g_idx, const void* bias, int32_t bias_dtype,
+                            int32_t N_out, int32_t K, int32_t n_groups, int32_t bits,
+                            int32_t group_size, void* y, void* stream);
+
+/* ---- flat round-to-nearest helpers ------------------------------------------
+ * Replace quantize_kernel / dequantize_kernel and the host loops around them
+ * (kernels/triton_kernels.py:34-123, 377-481).  Groups are runs of group_size
+ * consecutive elements of the flattened tensor; scale = (max-min)/maxq (1 if
+ * zero), zero = -min/scale (not rounded, :411).
+ */
+int32_t dgq_rtn_find_params(const float* x, int64_t n, int32_t bits, int32_t group_size,
+                            float* scales, float* zeros, void* stream);
+int32_t dgq_rtn_quantize(const float* x, int64_t n, int32_t bits, int32_t group_size,
+                         const float* scales, const float* zeros, uint8_t* q, void* stream);
+int32_t dgq_rtn_dequantize(const uint8_t* q, int64_t n, int32_t group_size,
+                           const float* scales, const float* zeros, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DGQ_H_ */

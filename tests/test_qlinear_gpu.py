@@ -1,0 +1,36 @@
+"""dgq_qlinear_forward against the oracle's dequantize + matmul."""
+import pytest
+import torch
+
+from oracle import oracle_gptq as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 7, 16, 33])
+@pytest.mark.parametrize("N_out,K,g,bits", [(64, 128, 32, 4), (100, 520, 128, 4), (37, 203, 64, 4),
+                                             (256, 1024, 128, 8), (64, 256, 64, 3), (48, 512, -1, 2)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_qlinear(dgq, M, N_out, K, g, bits, dtype):
+    gen = torch.Generator().manual_seed(M * 7 + N_out + K)
+    codes = torch.randint(0, 2 ** bits, (N_out, K), generator=gen).to(torch.uint8)
+    ng = O.n_groups(K, g)
+    scales = (torch.rand(N_out, ng, generator=gen) * 0.02 + 0.001).half()
+    zeros = torch.randint(0, 2 ** bits, (N_out, ng), generator=gen).half()
+    gg = K if g <= 0 else g
+    g_idx = (torch.arange(K) // gg).to(torch.int32)
+    g_idx = g_idx[torch.randperm(K, generator=gen)]            # act-order style mapping
+    bias = torch.randn(N_out, generator=gen).to(dtype)
+    x = torch.randn(M, K, generator=gen).to(dtype)
+    qw = O.pack_f2(codes, bits)
+    want = O.qlinear_forward(x, codes, scales, zeros, g_idx, bias, g)
+    got = dgq.qlinear_forward(x.cuda(), qw.cuda(), scales.cuda(), zeros.cuda(), g_idx.cuda(),
+                              bias.cuda(), K, bits, g)
+    assert got.dtype == dtype and tuple(got.shape) == (M, N_out)
+    tol = {torch.float32: 2e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype]
+    scale = want.abs().max()
+    assert float((got.float().cpu() - want).abs().max()) <= tol * float(scale)
+    # no g_idx, no bias
+    want2 = O.qlinear_forward(x, codes, scales, zeros, None, None, g)
+    got2 = dgq.qlinear_forward(x.cuda(), qw.cuda(), scales.cuda(), zeros.cuda(), None, None, K, bits, g)
+    assert float((got2.float().cpu() - want2).abs().max()) <= tol * float(want2.abs().max())
