@@ -79,7 +79,12 @@ def test_against_live_oracle(dgq, N_out, K, Tk, bits, g, act):
     W, X = synth_layer(N_out, K, Tk, N_out + K + bits)
     nseq = 4
     q, lin, stats = run_gpu(W, X, nseq, bits, g, 128, act)
-    H_raw = X.t() @ X
+    H_cpu = X.t() @ X
+    assert float((q.H.cpu() - H_cpu).norm() / H_cpu.norm()) <= 1e-3
+    # Stage-wise parity: the oracle quantizes with the Hessian the GPU accumulated.  With
+    # act-order, diagonal entries that agree to ~1e-6 would otherwise sort differently on
+    # the two sides and the column orders (hence the codes) would not be comparable.
+    H_raw = q.H.cpu().clone()
     ref = O.gptq_quantize(W, H_raw, nseq, bits, g, 128, 0.01, act)
     compare(q, lin, stats, W, H_raw, ref)
     assert stats["bits"] == bits and stats["group_size"] == g
@@ -92,7 +97,7 @@ def test_bf16_layer_and_pack_formats(dgq):
     Wb = W.bfloat16().float()
     q, lin, stats = run_gpu(Wb, X, 4, 4, 128, 128, True, dtype=torch.bfloat16)
     assert lin.weight.dtype == torch.bfloat16
-    H_raw = X.t() @ X
+    H_raw = q.H.cpu().clone()
     ref = O.gptq_quantize(Wb, H_raw, 4, 4, 128, 128, 0.01, True)
     diff = (q.codes.cpu().int() - ref["codes"].int()).abs()
     assert float((diff == 0).float().mean()) >= CODE_MATCH and int(diff.max()) <= 1
@@ -109,7 +114,7 @@ def test_dead_columns(dgq):
     X[:, 200] = 0
     for act in (False, True):
         q, lin, stats = run_gpu(W, X, 4, 4, 128, 128, act)
-        H_raw = X.t() @ X
+        H_raw = q.H.cpu().clone()
         ref = O.gptq_quantize(W, H_raw, 4, 4, 128, 128, 0.01, act)
         compare(q, lin, stats, W, H_raw, ref, f"dead act={act}")
 
@@ -129,7 +134,7 @@ def test_fasterquant_alias_and_quantizer(dgq):
     q = GPTQ(lin.cuda(), bits=4)
     q.add_batch(X.reshape(4, -1, 256).cuda(), None)
     st = q.fasterquant(blocksize=64, percdamp=0.02, group_size=64, actorder=True)
-    ref = O.gptq_quantize(W, X.t() @ X, 4, 4, 64, 64, 0.02, True)
+    ref = O.gptq_quantize(W, q.H.cpu().clone(), 4, 4, 64, 64, 0.02, True)
     diff = (q.codes.cpu().int() - ref["codes"].int()).abs()
     assert float((diff == 0).float().mean()) >= CODE_MATCH and st["group_size"] == 64
     qz = Quantizer(4)
