@@ -30,6 +30,7 @@ SIGNATURES = {
     "dgq_status_string": (ctypes.c_char_p, [_I32]),
     "dgq_version": (_I32, []),
     "dgq_device_check": (_I32, []),
+    "dgq_launch_count": (_I64, []),
     "dgq_hessian_accum": (_I32, [_P, _I64, _I32, _I64, _P, _I64, _F, _I32, _P, _P]),
     "dgq_cast_f32_to_bf16": (_I32, [_P, _P, _I64, _P]),
     "dgq_cast_f16_to_bf16": (_I32, [_P, _P, _I64, _P]),
@@ -101,6 +102,53 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class KernelTimers:
+    """Collects CUDA-event pairs around library calls, per call name, on the stream the
+    call is enqueued on.  Enable with :func:`set_timers`; read with :meth:`summary`."""
+
+    def __init__(self):
+        self.events = []
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b in self.events:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + a.elapsed_time(b))
+        return out
+
+
+_timers: Optional[KernelTimers] = None
+
+
+def set_timers(t: Optional[KernelTimers]) -> None:
+    global _timers
+    _timers = t
+
+
+class _timed:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _timers is not None:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+        return self
+
+    def __exit__(self, *exc):
+        if _timers is not None:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            _timers.events.append((self.name, self.a, b))
+        return False
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib().dgq_launch_count())
+
+
 def device_check() -> None:
     check(lib().dgq_device_check(), "dgq_device_check")
 
@@ -130,7 +178,7 @@ def to_bf16(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
     if x.numel() == 0:
         return out
-    with torch.cuda.device(x.device):
+    with torch.cuda.device(x.device), _timed("cast"):
         if x.dtype == torch.float32:
             check(lib().dgq_cast_f32_to_bf16(_ptr(x), _ptr(out), x.numel(), _stream()), "cast")
         elif x.dtype == torch.float16:
@@ -148,7 +196,7 @@ def hessian_accum(X: torch.Tensor, H: torch.Tensor, alpha: float = 1.0, splits: 
     assert H.dtype == torch.float32 and H.dim() == 2 and H.stride(1) == 1
     T, K = X.shape
     assert H.shape == (K, K)
-    with torch.cuda.device(X.device):
+    with torch.cuda.device(X.device), _timed("hessian_accum"):
         check(lib().dgq_hessian_accum(_ptr(X), T, K, X.stride(0), _ptr(H), H.stride(0), alpha,
                                       splits, _ptr(info), _stream()), "dgq_hessian_accum")
 
@@ -159,7 +207,7 @@ def actorder_perm(H: torch.Tensor, scale: float):
     K = H.shape[0]
     perm = torch.empty(K, dtype=torch.int32, device=H.device)
     inv = torch.empty(K, dtype=torch.int32, device=H.device)
-    with torch.cuda.device(H.device):
+    with torch.cuda.device(H.device), _timed("prepare"):
         check(lib().dgq_actorder_perm(_ptr(H), K, H.stride(0), scale, _ptr(perm), _ptr(inv),
                                       _stream()), "dgq_actorder_perm")
     return perm, inv
@@ -174,7 +222,7 @@ def hessian_prepare(H: torch.Tensor, scale: float, percdamp: float,
     dead = torch.empty(K, dtype=torch.uint8, device=H.device)
     nbytes = lib().dgq_hessian_prepare_workspace_bytes(K)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=H.device)
-    with torch.cuda.device(H.device):
+    with torch.cuda.device(H.device), _timed("prepare"):
         check(lib().dgq_hessian_prepare(_ptr(H), H.stride(0), _ptr(Hout), K, K, scale, percdamp,
                                         _ptr(perm), _ptr(dead), _ptr(ws), nbytes, _stream()),
               "dgq_hessian_prepare")
@@ -187,7 +235,7 @@ def permute_cols(src: torch.Tensor, perm: Optional[torch.Tensor],
     assert src.dim() == 2 and src.stride(1) == 1
     rows, cols = src.shape
     dst = torch.empty((rows, cols), dtype=src.dtype, device=src.device)
-    with torch.cuda.device(src.device):
+    with torch.cuda.device(src.device), _timed("permute"):
         if src.dtype == torch.float32:
             check(lib().dgq_permute_cols_f32(_ptr(src), src.stride(0), _ptr(dst), cols, rows, cols,
                                              _ptr(perm), _ptr(dead), _stream()), "permute_cols_f32")
@@ -206,7 +254,7 @@ def inv_chol_upper(A: torch.Tensor, info: Optional[torch.Tensor] = None) -> torc
     K = A.shape[0]
     nbytes = lib().dgq_inv_chol_workspace_bytes(K)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=A.device)
-    with torch.cuda.device(A.device):
+    with torch.cuda.device(A.device), _timed("inv_chol"):
         check(lib().dgq_inv_chol_upper(_ptr(A), K, A.stride(0), _ptr(info), _ptr(ws), nbytes,
                                        _stream()), "dgq_inv_chol_upper")
     return A
@@ -228,7 +276,7 @@ def gptq_quantize(W: torch.Tensor, U: torch.Tensor, bits: int, group_size: int, 
     nbytes = lib().dgq_gptq_quantize_workspace_bytes(N_out, K, blocksize)
     check(min(nbytes, 0), "dgq_gptq_quantize_workspace_bytes")
     ws = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
-    with torch.cuda.device(W.device):
+    with torch.cuda.device(W.device), _timed("gptq_quantize"):
         check(lib().dgq_gptq_quantize(_ptr(W), W.stride(0), _ptr(U), U.stride(0), N_out, K, bits,
                                       group_size, blocksize, _ptr(codes), K, _ptr(scales),
                                       _ptr(zeros), _ptr(terr), _ptr(ws), nbytes, _stream()),
@@ -282,7 +330,7 @@ def pack(codes: torch.Tensor, bits: int, fmt: int) -> torch.Tensor:
     codes = codes.contiguous()
     rows, cols = codes.shape
     out = _packed_tensor(rows, cols, bits, fmt, codes.device)
-    with torch.cuda.device(codes.device):
+    with torch.cuda.device(codes.device), _timed("pack"):
         check(lib().dgq_pack(_ptr(codes), rows, cols, bits, fmt, _ptr(out), _stream()), "dgq_pack")
     return out
 

@@ -1,5 +1,12 @@
 // Library-wide entry points: version, status strings, device check.
+#include <atomic>
+
 #include "common.cuh"
+
+static std::atomic<int64_t> g_launches{0};
+void dgq_note_launches(int64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+DGQ_EXPORT int64_t dgq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 DGQ_EXPORT int32_t dgq_version(void) { return 100; }
 

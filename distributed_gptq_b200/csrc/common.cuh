@@ -17,7 +17,12 @@
 
 static inline cudaStream_t dgq_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
-static inline int32_t dgq_launch_status() {
+// Process-wide count of kernels this library has launched (defined in abi.cu).
+void dgq_note_launches(int64_t n);
+
+// Status of the launches an entry point has just made; `launched` is how many.
+static inline int32_t dgq_launch_status(int64_t launched = 1) {
+  dgq_note_launches(launched);
   return cudaGetLastError() == cudaSuccess ? DGQ_OK : DGQ_ERR_LAUNCH;
 }
 

@@ -331,7 +331,7 @@ DGQ_EXPORT int32_t dgq_hessian_prepare(const float* H, int64_t ldh, float* Hout,
   prepare_diag_kernel<<<1, 256, 0, st>>>(H, ldh, K, scale, perm, dead_out, diag_sum);
   prepare_gather_kernel<<<dgq_grid((int64_t)K * K, 256), 256, 0, st>>>(H, ldh, Hout, ldo, K, scale,
                                                                       percdamp, perm, diag_sum);
-  return dgq_launch_status();
+  return dgq_launch_status(2);
 }
 
 DGQ_EXPORT int32_t dgq_permute_cols_f32(const float* src, int64_t lds, float* dst, int64_t ldd,

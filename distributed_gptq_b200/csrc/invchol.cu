@@ -169,5 +169,5 @@ DGQ_EXPORT int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t*
     copy_lower_block_kernel<<<1, 256, 0, st>>>(V.sub(k0, k0), nb, dinv);
   }
   zero_strict_lower_kernel<<<dgq_grid((int64_t)K * K, 256), 256, 0, st>>>(A, K, lda);
-  return dgq_launch_status();
+  return dgq_launch_status(2 * (int64_t)nblk + 1);  // + the matrix products counted as they go
 }

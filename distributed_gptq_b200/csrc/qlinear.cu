@@ -178,5 +178,5 @@ DGQ_EXPORT int32_t dgq_qlinear_forward(const void* x, int32_t x_dtype, int32_t M
   if (x_dtype == DGQ_F32) launch_all<float>(a, st);
   else if (x_dtype == DGQ_F16) launch_all<__half>(a, st);
   else launch_all<__nv_bfloat16>(a, st);
-  return dgq_launch_status();
+  return dgq_launch_status(dgq_cdiv(M, 16));
 }

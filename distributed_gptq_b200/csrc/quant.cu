@@ -249,5 +249,5 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
       launch_gemm<0>(g, st);
     }
   }
-  return dgq_launch_status();
+  return dgq_launch_status(dgq_cdiv(K, blocksize));
 }

@@ -136,7 +136,7 @@ class GPTQ:
         if inp.dim() == 2 and not isinstance(self.layer, nn.Conv2d):
             inp = inp.unsqueeze(0)
         batch = inp.shape[0]
-        x = self._tokens(inp.to(self.device))
+        x = self._tokens(inp.to(self.device, non_blocking=True))
         K = self.columns
         assert x.shape[1] == K, f"expected {K} input features, got {x.shape[1]}"
         K8 = _round_up(K, 8)
@@ -239,9 +239,13 @@ class GPTQ:
             "shape": self.codes.shape,
         }
 
-    def free(self) -> None:
+    def free_hessian(self) -> None:
+        """Drops the Hessian buffer (its memory returns to torch's caching allocator)."""
         self._Hbuf = None
         self._info = None
+
+    def free(self) -> None:
+        self.free_hessian()
         torch.cuda.empty_cache()
 
 

@@ -1,0 +1,114 @@
+"""Runs one kernel of the library a few times on a small seeded case, for profilers.
+
+    python -m distributed_gptq_b200.profile_case hessian   --K 4096 --T 32768
+    python -m distributed_gptq_b200.profile_case inv_chol  --K 4096
+    python -m distributed_gptq_b200.profile_case quantize  --K 4096 --N 4096
+    python -m distributed_gptq_b200.profile_case pack      --K 8192 --N 16384
+    python -m distributed_gptq_b200.profile_case dequant   --K 8192 --N 16384
+    python -m distributed_gptq_b200.profile_case qlinear   --K 5120 --N 5120 --M 16
+
+Prints the CUDA-event time of each repetition and the derived rate (algorithmic flops
+or bytes over time).  Sizes default to a few hundred MB so that a profiler capture ends
+quickly while the inputs still exceed the L2 cache.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import _C
+
+
+def _time(fn, reps):
+    out = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["hessian", "inv_chol", "quantize", "pack", "dequant", "qlinear"])
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--N", type=int, default=4096)
+    ap.add_argument("--T", type=int, default=32768)
+    ap.add_argument("--M", type=int, default=16)
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--splits", type=int, default=0)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    _C.device_check()
+    g = torch.Generator(device=dev).manual_seed(0)
+    K, N, T = a.K, a.N, a.T
+    if a.case == "hessian":
+        X = torch.randn(T, K, generator=g, device=dev).to(torch.bfloat16)
+        H = torch.zeros((K, K), dtype=torch.float32, device=dev)
+        ts = _time(lambda: _C.hessian_accum(X, H, 1.0, a.splits), a.reps)
+        P = -(-K // 256)
+        ex = (P * (P + 1) // 2) * 2.0 * 256 * 256 * T
+        for t in ts:
+            print(f"hessian K={K} T={T}: {t:.3f} ms  executed {ex / t / 1e9:.1f} TFLOP/s  "
+                  f"algorithmic {2.0 * T * K * K / t / 1e9:.1f} TFLOP/s")
+    elif a.case in ("inv_chol", "quantize"):
+        X = torch.randn(2 * K, K, generator=g, device=dev).to(torch.bfloat16)
+        H = torch.zeros((K, K), dtype=torch.float32, device=dev)
+        _C.hessian_accum(X, H)
+        Hp, _ = _C.hessian_prepare(H, 1.0, 0.01, None)
+        if a.case == "inv_chol":
+            A = Hp.clone()
+
+            def f():
+                A.copy_(Hp)
+                _C.inv_chol_upper(A)
+            for t in _time(f, a.reps):
+                print(f"inv_chol K={K}: {t:.3f} ms (incl. one K^2 copy)  {2 * K ** 3 / 3 / t / 1e9:.2f} TFLOP/s")
+        else:
+            U = _C.inv_chol_upper(Hp)
+            W0 = torch.randn(N, K, generator=g, device=dev) * 0.02
+            W = W0.clone()
+
+            def f():
+                W.copy_(W0)
+                _C.gptq_quantize(W, U, a.bits, 128, 128)
+            for t in _time(f, a.reps):
+                print(f"gptq_quantize N={N} K={K}: {t:.3f} ms  trailing update "
+                      f"{N * K * (K - 128) / t / 1e9:.2f} TFLOP/s")
+    elif a.case in ("pack", "dequant"):
+        codes = torch.randint(0, 2 ** a.bits, (N, K), generator=g, device=dev, dtype=torch.uint8)
+        if a.case == "pack":
+            for t in _time(lambda: _C.pack(codes, a.bits, _C.FMT_BYTES_LO_FIRST), a.reps):
+                nbytes = N * K * (1 + a.bits / 8)
+                print(f"pack N={N} K={K} bits={a.bits}: {t:.3f} ms  {nbytes / t / 1e6:.1f} GB/s")
+        else:
+            packed = _C.pack(codes, a.bits, _C.FMT_BYTES_LO_FIRST)
+            ng = K // 128
+            s = torch.rand(N, ng, generator=g, device=dev).half()
+            z = torch.randint(0, 2 ** a.bits, (N, ng), generator=g, device=dev).half()
+            fn = lambda: _C.unpack_dequant(packed, s, z, None, K, a.bits, 128,
+                                           _C.FMT_BYTES_LO_FIRST, torch.bfloat16)
+            for t in _time(fn, a.reps):
+                nbytes = N * K * (a.bits / 8 + 2) + 4 * N * ng
+                print(f"unpack_dequant N={N} K={K} bits={a.bits}: {t:.3f} ms  {nbytes / t / 1e6:.1f} GB/s")
+    else:
+        codes = torch.randint(0, 16, (N, K), generator=g, device=dev, dtype=torch.uint8)
+        qw = _C.pack(codes, 4, _C.FMT_BYTES_LO_FIRST)
+        ng = K // 128
+        s = torch.rand(N, ng, generator=g, device=dev).half() * 0.01
+        z = torch.randint(0, 16, (N, ng), generator=g, device=dev).half()
+        x = torch.randn(a.M, K, generator=g, device=dev).to(torch.bfloat16)
+        fn = lambda: _C.qlinear_forward(x, qw, s, z, None, None, K, 4, 128)
+        for t in _time(fn, a.reps):
+            nbytes = N * K / 2 + 4 * N * ng + 2 * a.M * (K + N)
+            print(f"qlinear M={a.M} N={N} K={K}: {t * 1e3:.1f} us  {nbytes / t / 1e6:.1f} GB/s")
+
+
+if __name__ == "__main__":
+    main()

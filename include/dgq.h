@@ -55,6 +55,10 @@ const char* dgq_status_string(int32_t status);
 int32_t     dgq_version(void);
 /* 0 when the current device can run this library (compute capability 10.x). */
 int32_t     dgq_device_check(void);
+/* Number of CUDA kernels this library has launched in this process so far.  It has
+ * no counterpart in the reference; the benchmark reports it as evidence that the
+ * timed work ran in these kernels. */
+int64_t     dgq_launch_count(void);
 
 /* ---- Hessian accumulation ------------------------------------------------
  * Replaces GPTQ.add_batch, core/gptq.py:63-89 (`self.H += inp @ inp.t()`).
