@@ -270,17 +270,21 @@ hessian_syrk_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
 // Chooses how many token ranges to cut the work into: the fewest that fills the
 // last wave of CTAs well, keeping every range at least `min_tokens` long.
 int choose_splits(int n_tiles, int64_t T, int sms) {
+  // Cost of a split count s, in token-times of one tile: every wave of CTAs streams
+  // T/s tokens and then pays one epilogue, which is not overlapped with the next tile
+  // and costs about as much as streaming EPILOGUE_TOKENS tokens (measured on B200).
+  const double EPILOGUE_TOKENS = 1700.0;
   const int64_t min_tokens = 2048;
   int max_splits = (int)std::max<int64_t>(1, T / min_tokens);
   if (max_splits > 64) max_splits = 64;
   int best = 1;
-  double best_eff = 0.0;
+  double best_cost = 0.0;
   for (int s = 1; s <= max_splits; ++s) {
-    int64_t items = (int64_t)n_tiles * s;
-    int64_t waves = dgq_cdiv(items, sms);
-    double eff = (double)items / (double)(waves * sms);
-    if (eff > best_eff + 0.02) {  // prefer fewer splits unless clearly better
-      best_eff = eff;
+    const int64_t items = (int64_t)n_tiles * s;
+    const int64_t waves = dgq_cdiv(items, sms);
+    const double cost = (double)waves * ((double)T / s + EPILOGUE_TOKENS);
+    if (s == 1 || cost < 0.97 * best_cost) {  // prefer fewer splits unless clearly better
+      best_cost = cost;
       best = s;
     }
   }

@@ -1,19 +1,24 @@
 // Blockwise GPTQ quantization of one weight matrix given the inverse-Hessian factor.
 //
 // For every block of `blocksize` (<= 128) columns:
-//   1. gptq_block_kernel - one warp per weight row.  Lane l keeps columns l, l+32,
-//      l+64, l+96 of the block in registers; the block of U sits in shared memory.
-//      Columns are visited in order: the owning lane's value is broadcast with a
-//      shuffle, every lane evaluates the quantize/dequantize formulas on it (so the
-//      scaled error needs no second broadcast) and applies the error feedback to the
-//      columns it holds.  Codes, dequantized values and the scaled errors leave
-//      through coalesced stores.
+//   1. gptq_block8_kernel - eight lanes per weight row, four rows per warp.  A lane
+//      keeps 16 columns of the 128-column block in registers (four float4 chunks,
+//      interleaved over the lanes so that shared-memory reads of the block of U are
+//      conflict free).  Columns are visited in order, the loop fully unrolled: the
+//      owning lane's value is broadcast inside its group of eight with a shuffle,
+//      every lane of the group evaluates the quantize/dequantize formulas on it (so
+//      the scaled error needs no second broadcast) and applies the error feedback
+//      to the columns it holds.  Codes, dequantized values and the scaled errors
+//      leave through 16-byte stores.  (gptq_block_kernel, one warp per row, is the
+//      general variant for ragged blocks and groups narrower than 32 columns.)
 //   2. trailing update - W[:, i2:] -= Err * U[i1:i2, i2:]  (fp32 matrix product).
 //
 // Group scale/zero are taken from W as it stands when the group's first column is
 // reached by the block loop (all earlier blocks' trailing updates applied, none of
 // the current block's in-block updates), which for groups that start inside a block
 // means the values the block had at entry.
+#include <algorithm>
+
 #include "common.cuh"
 #include "sgemm_view.cuh"
 
@@ -190,6 +195,129 @@ gptq_block_kernel(const QuantArgs a) {
   if (lane == 0 && err_sq != 0.0) atomicAdd(a.total_error, err_sq);
 }
 
+// ---- fast variant: full 128-column blocks, groups of 32 / 64 / >= 128 columns ----------------
+constexpr int F_WARPS = 8;
+constexpr int F_ROWS_PER_CTA = F_WARPS * 4;
+
+template <int GPB /* groups per block: 1, 2 or 4 */>
+__global__ void __launch_bounds__(F_WARPS * 32)
+gptq_block8_kernel(const QuantArgs a) {
+  extern __shared__ float Us[];  // 128 x 128, row j = U[i1 + j][i1 .. i1 + 128), zeros left of the diagonal
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int sub = lane & 7;   // lane inside the row's group of eight
+  const int rg = lane >> 3;   // row inside the warp
+  for (int idx = threadIdx.x; idx < MAX_BLOCK * MAX_BLOCK / 4; idx += blockDim.x) {
+    const int j = idx / (MAX_BLOCK / 4), c4 = (idx % (MAX_BLOCK / 4)) * 4;
+    const float4 u = *reinterpret_cast<const float4*>(a.U + (int64_t)(a.i1 + j) * a.ldu + a.i1 + c4);
+    float4 v;
+    v.x = (c4 + 0 >= j) ? u.x : 0.f; v.y = (c4 + 1 >= j) ? u.y : 0.f;
+    v.z = (c4 + 2 >= j) ? u.z : 0.f; v.w = (c4 + 3 >= j) ? u.w : 0.f;
+    reinterpret_cast<float4*>(Us)[idx] = v;
+  }
+  __syncthreads();
+  const float4* Us4 = reinterpret_cast<const float4*>(Us);
+  constexpr int GW = MAX_BLOCK / GPB;  // columns per group inside the block
+
+  double err_sq = 0.0;
+  for (int row0 = blockIdx.x * F_ROWS_PER_CTA + warp * 4; row0 < a.N_out;
+       row0 += gridDim.x * F_ROWS_PER_CTA) {
+    const int row = row0 + rg;
+    const bool live = row < a.N_out;
+    const int rrow = live ? row : a.N_out - 1;  // idle lanes shadow the last row, never store
+    float* wrow = a.W + (int64_t)rrow * a.ldw + a.i1;
+    float w[16], what[16], ev[16];
+    uint32_t code[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 t = *reinterpret_cast<const float4*>(wrow + 4 * (sub + 8 * i));
+      w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
+    }
+    // ---- scale / zero of the groups of this block
+    float sg[GPB], zg[GPB];
+    if (GPB == 1 && a.group > MAX_BLOCK && (a.i1 % a.group) != 0) {
+      sg[0] = a.scales[(int64_t)rrow * a.n_groups + a.i1 / a.group];
+      zg[0] = a.zeros[(int64_t)rrow * a.n_groups + a.i1 / a.group];
+    } else {
+#pragma unroll
+      for (int g = 0; g < GPB; ++g) {
+        float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if ((32 * i) / GW == g) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { mn = fminf(mn, w[4 * i + e]); mx = fmaxf(mx, w[4 * i + e]); }
+          }
+        }
+        if (GPB == 1 && a.group > MAX_BLOCK) {
+          // the group continues past this block: the rest of it is read from W
+          const int gend = min(a.group, a.K - a.i1);
+          for (int c = MAX_BLOCK + sub; c < gend; c += 8) {
+            const float v = wrow[c];
+            mn = fminf(mn, v); mx = fmaxf(mx, v);
+          }
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+          mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        dgq_scale_zero(mn, mx, a.maxq, sg[g], zg[g]);
+        if (live && sub == 0) {
+          const int gi = a.i1 / a.group + g;
+          a.scales[(int64_t)row * a.n_groups + gi] = sg[g];
+          a.zeros[(int64_t)row * a.n_groups + gi] = zg[g];
+        }
+      }
+    }
+    // ---- the column loop, fully unrolled: every register index below is a constant
+#pragma unroll
+    for (int j = 0; j < MAX_BLOCK; ++j) {
+      const int ij = j >> 5;            // which of the lane's four chunks holds column j
+      const int owner = (j >> 2) & 7;   // lane of the group that holds it
+      const int reg = 4 * ij + (j & 3);
+      const float wj = __shfl_sync(0xffffffffu, w[reg], owner, 8);
+      const float sj = sg[j / GW], zj = zg[j / GW];
+      const float q = dgq_quant_level(wj, sj, zj, a.maxq);
+      const float wh = dgq_dequant_level(q, sj, zj);
+      const float e = __fdiv_rn(__fsub_rn(wj, wh), Us[j * MAX_BLOCK + j]);
+      if (sub == owner) {
+        what[reg] = wh;
+        ev[reg] = e;
+        code[ij] |= ((uint32_t)q) << (8 * (j & 3));
+      }
+      // error feedback; U is zero left of the diagonal, so columns already done are untouched
+#pragma unroll
+      for (int i = ij; i < 4; ++i) {
+        const float4 u = Us4[j * (MAX_BLOCK / 4) + sub + 8 * i];
+        w[4 * i + 0] = fmaf(-e, u.x, w[4 * i + 0]);
+        w[4 * i + 1] = fmaf(-e, u.y, w[4 * i + 1]);
+        w[4 * i + 2] = fmaf(-e, u.z, w[4 * i + 2]);
+        w[4 * i + 3] = fmaf(-e, u.w, w[4 * i + 3]);
+      }
+    }
+    // ---- outputs
+    if (live) {
+      float* erow = a.err + (int64_t)row * MAX_BLOCK;
+      uint8_t* crow = a.codes + (int64_t)row * a.ldc + a.i1;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = 4 * (sub + 8 * i);
+        *reinterpret_cast<float4*>(wrow + c) =
+            make_float4(what[4 * i], what[4 * i + 1], what[4 * i + 2], what[4 * i + 3]);
+        *reinterpret_cast<float4*>(erow + c) =
+            make_float4(ev[4 * i], ev[4 * i + 1], ev[4 * i + 2], ev[4 * i + 3]);
+        *reinterpret_cast<uint32_t*>(crow + c) = code[i];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) err_sq += (double)ev[4 * i + e] * (double)ev[4 * i + e];
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) err_sq += __shfl_xor_sync(0xffffffffu, err_sq, o);
+  if (lane == 0 && err_sq != 0.0) atomicAdd(a.total_error, err_sq);
+}
+
 bool valid_bits(int b) { return b == 2 || b == 3 || b == 4 || b == 8; }
 
 }  // namespace
@@ -222,11 +350,21 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   static bool attr_set = false;
   const size_t smem = (size_t)MAX_BLOCK * MAX_BLOCK * sizeof(float);
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gptq_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
+    const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    if (cudaFuncSetAttribute(gptq_block_kernel, at, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(gptq_block8_kernel<1>, at, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(gptq_block8_kernel<2>, at, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(gptq_block8_kernel<4>, at, (int)smem) != cudaSuccess)
       return DGQ_ERR_LAUNCH;
     attr_set = true;
   }
+  // the fast kernel takes full 128-column blocks with 16-byte aligned rows
+  const bool fast_layout = blocksize == MAX_BLOCK && ldw % 4 == 0 && ldu % 4 == 0 && ldc % 4 == 0 &&
+                           dgq_aligned(W, 16) && dgq_aligned(U, 16) && dgq_aligned(codes, 4);
+  int gpb = 0;  // groups per block for the fast kernel, 0 = not eligible
+  if (group >= MAX_BLOCK) gpb = (group % MAX_BLOCK == 0 || per_channel) ? 1 : 0;
+  else if (group == 64) gpb = 2;
+  else if (group == 32) gpb = 4;
   if (cudaMemsetAsync(total_error, 0, sizeof(double), st) != cudaSuccess) return DGQ_ERR_LAUNCH;
 
   QuantArgs a;
@@ -241,12 +379,20 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   for (int i1 = 0; i1 < K; i1 += blocksize) {
     a.i1 = i1;
     a.bw = std::min(blocksize, K - i1);
-    gptq_block_kernel<<<grid, ROWS_PER_CTA * 32, (size_t)a.bw * MAX_BLOCK * sizeof(float), st>>>(a);
+    if (fast_layout && gpb != 0 && a.bw == MAX_BLOCK) {
+      const unsigned fgrid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, F_ROWS_PER_CTA),
+                                                         (int64_t)dgq_sm_count() * 3);
+      if (gpb == 1) gptq_block8_kernel<1><<<fgrid, F_WARPS * 32, smem, st>>>(a);
+      else if (gpb == 2) gptq_block8_kernel<2><<<fgrid, F_WARPS * 32, smem, st>>>(a);
+      else gptq_block8_kernel<4><<<fgrid, F_WARPS * 32, smem, st>>>(a);
+    } else {
+      gptq_block_kernel<<<grid, ROWS_PER_CTA * 32, (size_t)a.bw * MAX_BLOCK * sizeof(float), st>>>(a);
+    }
     const int i2 = i1 + a.bw;
     if (i2 < K) {
-      GemmArgs g{a.err, MAX_BLOCK, 1, U + (int64_t)i1 * ldu + i2, ldu, 1,
-                 W + i2, ldw, 1, N_out, K - i2, a.bw, -1.f, 1.f};
-      launch_gemm<0>(g, st);
+      GemmArgs g = gemm_args(a.err, MAX_BLOCK, 1, U + (int64_t)i1 * ldu + i2, ldu, 1,
+                             W + i2, ldw, 1, N_out, K - i2, a.bw, -1.f, 1.f);
+      launch_gemm(g, st);
     }
   }
   return dgq_launch_status(dgq_cdiv(K, blocksize));
