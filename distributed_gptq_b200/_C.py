@@ -41,6 +41,7 @@ SIGNATURES = {
     "dgq_permute_cols_u8": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _P, _P]),
     "dgq_inv_chol_workspace_bytes": (_I64, [_I32]),
     "dgq_inv_chol_upper": (_I32, [_P, _I32, _I64, _P, _P, _I64, _P]),
+    "dgq_gemm_f32": (_I32, [_P, _I64, _P, _I64, _I32, _P, _I64, _I32, _I32, _I32, _F, _F, _I32, _P, _P]),
     "dgq_gptq_quantize_workspace_bytes": (_I64, [_I32, _I32, _I32]),
     "dgq_gptq_quantize": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _P, _I64,
                                  _P, _P, _P, _P, _I64, _P]),
@@ -258,6 +259,22 @@ def inv_chol_upper(A: torch.Tensor, info: Optional[torch.Tensor] = None) -> torc
         check(lib().dgq_inv_chol_upper(_ptr(A), K, A.stride(0), _ptr(info), _ptr(ws), nbytes,
                                        _stream()), "dgq_inv_chol_upper")
     return A
+
+
+def gemm_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, b_is_kn: bool, alpha: float = 1.0,
+             beta: float = 0.0, lower_only: bool = False,
+             info: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``c = alpha * a @ (b if b_is_kn else b.T) + beta * c`` on the tensor cores, fp32-accurate."""
+    _require_cuda(a, b, c)
+    m, k = a.shape
+    n = c.shape[1]
+    assert c.shape[0] == m and b.shape == ((k, n) if b_is_kn else (n, k))
+    assert a.stride(1) == 1 and b.stride(1) == 1 and c.stride(1) == 1
+    with torch.cuda.device(a.device), _timed("gemm_f32"):
+        check(lib().dgq_gemm_f32(_ptr(a), a.stride(0), _ptr(b), b.stride(0), int(b_is_kn), _ptr(c),
+                                 c.stride(0), m, n, k, alpha, beta, int(lower_only), _ptr(info),
+                                 _stream()), "dgq_gemm_f32")
+    return c
 
 
 def gptq_quantize(W: torch.Tensor, U: torch.Tensor, bits: int, group_size: int, blocksize: int):

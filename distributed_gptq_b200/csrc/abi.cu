@@ -1,10 +1,16 @@
 // Library-wide entry points: version, status strings, device check.
 #include <atomic>
+#include <cstdlib>
 
 #include "common.cuh"
 
 static std::atomic<int64_t> g_launches{0};
 void dgq_note_launches(int64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+bool dgq_use_tensor_gemm() {
+  const char* e = std::getenv("DGQ_SIMT_GEMM");
+  return !(e && e[0] != '\0' && e[0] != '0');
+}
 
 DGQ_EXPORT int64_t dgq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

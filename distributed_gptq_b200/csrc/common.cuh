@@ -26,6 +26,10 @@ static inline int32_t dgq_launch_status(int64_t launched = 1) {
   return cudaGetLastError() == cudaSuccess ? DGQ_OK : DGQ_ERR_LAUNCH;
 }
 
+// False when the environment variable DGQ_SIMT_GEMM is set to a non-zero value: the fp32
+// products of the inverse factor and of the trailing update then stay on the CUDA cores.
+bool dgq_use_tensor_gemm();
+
 static inline bool dgq_aligned(const void* p, uintptr_t a) {
   return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
 }

@@ -18,15 +18,18 @@
 //     V22 -= T * T^T                           (Schur complement, lower part)
 //     X22 = inv_chol(V22)                      (recursion)
 //     V21 = -X22 * (T * X11)                   (block of the inverse)
-//   leaves (<= 64 x 64) are factored and inverted by one small CTA in registers.
+//   leaves (<= 64 x 64) are factored and inverted by one small CTA in shared memory.
 //
-// All products are large, independent-tile matrix products (sgemm_view.cuh) whose
-// reduction ranges are clipped to the non-zero part of the triangular operands.
+// All products are independent-tile matrix products whose reduction ranges are clipped
+// to the non-zero part of the triangular operands: on the tensor cores with the
+// split-fp32 scheme of tgemm.cu when both output dimensions reach 128, on the CUDA
+// cores (sgemm_view.cuh) below that.
 #include <algorithm>
 #include <vector>
 
 #include "common.cuh"
 #include "sgemm_view.cuh"
+#include "tgemm.cuh"
 
 namespace {
 
@@ -57,68 +60,60 @@ reverse_out_kernel(const float* __restrict__ V, int64_t ldv, float* __restrict__
 }
 
 // ---- leaf: Cholesky + inverse of one diagonal block ------------------------------------------
-// 64 threads.  D (nb x nb, nb <= 64, lower part read) is replaced by inv(chol(D)) (lower;
-// the part above the diagonal is written as zeros).  Thread i owns row i of the block
-// in registers during the factorisation and column i of the inverse afterwards; all
-// loops are fully unrolled so the register arrays are never indexed dynamically.
+// 64 threads, the block lives in shared memory.  D (nb x nb, nb <= 64, lower part read) is
+// replaced by inv(chol(D)) (lower; the part above the diagonal is written as zeros).
+// Factorisation: right-looking, thread t owns row t; per column one division by the
+// pivot's square root (every thread takes the root itself, so the pivot needs no
+// broadcast step) and a rank-1 update of the row's remaining entries.  Inverse:
+// thread t solves L x = e_t for column t by forward substitution; all threads walk the
+// same row of L at the same time (a broadcast read) against their own column of X.
+// The loops are ordinary loops: the code stays small enough to live in the instruction
+// cache, which matters for a kernel that sits on the critical path ~K/64 times.
 __global__ void __launch_bounds__(NB)
 leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
   __shared__ float S[NB][NB + 1];
-  __shared__ float col[2][NB];
-  __shared__ float piv;
+  __shared__ float X[NB][NB + 1];
   const int t = threadIdx.x;
   for (int idx = t; idx < NB * NB; idx += NB) {
     const int i = idx / NB, j = idx % NB;
     S[i][j] = (i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f) : (i == j ? 1.f : 0.f);
   }
   __syncthreads();
-  float a[NB];
-#pragma unroll
-  for (int j = 0; j < NB; ++j) a[j] = S[t][j];
-
-#pragma unroll
   for (int k = 0; k < NB; ++k) {
-    if (t == k) {
-      float d = a[k];
-      if (!(d > 0.f) || !isfinite(d)) {
-        if (info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
-          info[1] = pivot_base - k;
-        d = 1.f;
-      }
-      piv = sqrtf(d);
+    float d = S[k][k];
+    if (!(d > 0.f) || !isfinite(d)) {
+      if (t == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
+        info[1] = pivot_base - k;
+      d = 1.f;
+    }
+    const float r = sqrtf(d);
+    float lik = 0.f;
+    if (t >= k) {
+      lik = (t == k) ? r : __fdiv_rn(S[t][k], r);
+      S[t][k] = lik;
     }
     __syncthreads();
-    const float d = piv;
-    if (t == k) a[k] = d;
-    if (t > k) a[k] = __fdiv_rn(a[k], d);
-    col[k & 1][t] = (t > k) ? a[k] : 0.f;
+    if (t > k) {
+#pragma unroll 4
+      for (int j = k + 1; j <= t; ++j) S[t][j] = fmaf(-lik, S[j][k], S[t][j]);
+    }
     __syncthreads();
-    const float lik = a[k];
-#pragma unroll
-    for (int j = k + 1; j < NB; ++j)
-      if (j <= t) a[j] = fmaf(-lik, col[k & 1][j], a[j]);
   }
-  // L back to shared memory (row t), zeros above the diagonal
-  __syncthreads();
-#pragma unroll
-  for (int j = 0; j < NB; ++j) S[t][j] = (j <= t) ? a[j] : 0.f;
-  __syncthreads();
-  // column t of X = L^-1 by forward substitution; entries above the diagonal come out 0
-  float x[NB];
-#pragma unroll
+  // X = L^-1, column t; entries above the diagonal come out as exact zeros
   for (int i = 0; i < NB; ++i) {
-    float acc = (i == t) ? 1.f : 0.f;
-#pragma unroll
-    for (int k = 0; k < i; ++k) acc = fmaf(-S[i][k], x[k], acc);
-    x[i] = (i >= t) ? __fdiv_rn(acc, S[i][i]) : 0.f;
+    float acc0 = (i == t) ? 1.f : 0.f, acc1 = 0.f;
+    int k = 0;
+    for (; k + 1 < i; k += 2) {
+      acc0 = fmaf(-S[i][k], X[k][t], acc0);
+      acc1 = fmaf(-S[i][k + 1], X[k + 1][t], acc1);
+    }
+    if (k < i) acc0 = fmaf(-S[i][k], X[k][t], acc0);
+    X[i][t] = (i >= t) ? __fdiv_rn(acc0 + acc1, S[i][i]) : 0.f;
   }
-  __syncthreads();
-#pragma unroll
-  for (int i = 0; i < NB; ++i) S[i][t] = x[i];
   __syncthreads();
   for (int idx = t; idx < NB * NB; idx += NB) {
     const int i = idx / NB, j = idx % NB;
-    if (i < nb && j < nb) D[(int64_t)i * ldd + j] = S[i][j];
+    if (i < nb && j < nb) D[(int64_t)i * ldd + j] = X[i][j];
   }
 }
 
@@ -130,6 +125,7 @@ struct Plan {
   int32_t* info;
   cudaStream_t st;
   int64_t leaves;
+  bool use_tensor;
 };
 
 int split_point(int n) {
@@ -147,6 +143,25 @@ void rec_workspace(int n, int depth, std::vector<int64_t>& need, int64_t& t2) {
   rec_workspace(m2, depth + 1, need, t2);
 }
 
+// One product of the recursion.  B is (n, k) row-major when !b_is_kn, (k, n) when b_is_kn.
+void mm(Plan& p, const float* a, int64_t lda, const float* b, int64_t ldb, bool b_is_kn, float* c,
+        int64_t ldc, int m, int n, int k, float alpha, float beta, int lo_from_j, int hi_from_j,
+        int hi_from_i, int lower_only) {
+  if (p.use_tensor && m >= dgq::TGEMM_TILE && n >= dgq::TGEMM_TILE) {
+    dgq::TGemmArgs t;
+    t.a = a; t.lda = lda; t.b = b; t.ldb = ldb; t.c = c; t.ldc = ldc;
+    t.m = m; t.n = n; t.k = k; t.alpha = alpha; t.beta = beta; t.b_is_kn = b_is_kn ? 1 : 0;
+    t.lo_from_j = lo_from_j; t.hi_from_j = hi_from_j; t.hi_from_i = hi_from_i;
+    t.lower_only = lower_only; t.info = p.info;
+    if (dgq::tgemm_supported(t) && dgq::tgemm_launch(t, p.st)) return;
+  }
+  GemmArgs g = b_is_kn ? gemm_args(a, lda, 1, b, ldb, 1, c, ldc, 1, m, n, k, alpha, beta)
+                       : gemm_args(a, lda, 1, b, 1, ldb, c, ldc, 1, m, n, k, alpha, beta);
+  g.lo_from_j = lo_from_j; g.hi_from_j = hi_from_j; g.hi_from_i = hi_from_i;
+  g.lower_only = lower_only;
+  launch_gemm(g, p.st);
+}
+
 void rec(Plan& p, int o, int n, int depth) {
   float* V = p.V;
   const int64_t ld = p.ldv;
@@ -161,27 +176,15 @@ void rec(Plan& p, int o, int n, int depth) {
   float* V22 = V + (int64_t)(o + h) * ld + (o + h);
   float* T1 = p.T1[depth];
   rec(p, o, h, depth + 1);
-  {  // T1 = V21 * X11^T : B(k,j) = X11[j][k], non-zero for k <= j
-    GemmArgs g = gemm_args(V21, ld, 1, V11, 1, ld, T1, h, 1, m2, h, h, 1.f, 0.f);
-    g.hi_from_j = 1;
-    launch_gemm(g, p.st);
-  }
-  {  // V22 -= T1 * T1^T, lower part
-    GemmArgs g = gemm_args(T1, h, 1, T1, 1, h, V22, ld, 1, m2, m2, h, -1.f, 1.f);
-    g.lower_only = 1;
-    launch_gemm(g, p.st);
-  }
+  // T1 = V21 * X11^T : X11[j][k] is non-zero for k <= j
+  mm(p, V21, ld, V11, ld, false, T1, h, m2, h, h, 1.f, 0.f, 0, 1, 0, 0);
+  // V22 -= T1 * T1^T, lower part
+  mm(p, T1, h, T1, h, false, V22, ld, m2, m2, h, -1.f, 1.f, 0, 0, 0, 1);
   rec(p, o + h, m2, depth + 1);
-  {  // T2 = T1 * X11 : B(k,j) = X11[k][j], non-zero for k >= j
-    GemmArgs g = gemm_args(T1, h, 1, V11, ld, 1, p.T2, h, 1, m2, h, h, 1.f, 0.f);
-    g.lo_from_j = 1;
-    launch_gemm(g, p.st);
-  }
-  {  // V21 = -X22 * T2 : A = X22 lower triangular, non-zero for k <= i
-    GemmArgs g = gemm_args(V22, ld, 1, p.T2, h, 1, V21, ld, 1, m2, h, m2, -1.f, 0.f);
-    g.hi_from_i = 1;
-    launch_gemm(g, p.st);
-  }
+  // T2 = T1 * X11 : X11[k][j] is non-zero for k >= j
+  mm(p, T1, h, V11, ld, true, p.T2, h, m2, h, h, 1.f, 0.f, 1, 0, 0, 0);
+  // V21 = -X22 * T2 : X22[i][k] is non-zero for k <= i
+  mm(p, V22, ld, p.T2, h, true, V21, ld, m2, h, m2, -1.f, 0.f, 0, 0, 1, 0);
 }
 
 int64_t round4(int64_t x) { return (x + 3) / 4 * 4; }
@@ -208,6 +211,7 @@ DGQ_EXPORT int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t*
   p.K = K;
   p.info = info;
   p.leaves = 0;
+  p.use_tensor = dgq_use_tensor_gemm();
   p.ldv = round4(K);
   float* w = reinterpret_cast<float*>(ws);
   p.V = w;

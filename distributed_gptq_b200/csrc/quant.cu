@@ -11,7 +11,8 @@
 //      to the columns it holds.  Codes, dequantized values and the scaled errors
 //      leave through 16-byte stores.  (gptq_block_kernel, one warp per row, is the
 //      general variant for ragged blocks and groups narrower than 32 columns.)
-//   2. trailing update - W[:, i2:] -= Err * U[i1:i2, i2:]  (fp32 matrix product).
+//   2. trailing update - W[:, i2:] -= Err * U[i1:i2, i2:], an fp32-accurate product on
+//      the tensor cores (tgemm.cu; on the CUDA cores for ragged or tiny shapes).
 //
 // Group scale/zero are taken from W as it stands when the group's first column is
 // reached by the block loop (all earlier blocks' trailing updates applied, none of
@@ -21,6 +22,7 @@
 
 #include "common.cuh"
 #include "sgemm_view.cuh"
+#include "tgemm.cuh"
 
 namespace {
 
@@ -376,6 +378,7 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   a.N_out = N_out; a.K = K; a.group = group; a.maxq = (float)((1 << bits) - 1);
   const unsigned grid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, ROWS_PER_CTA),
                                                     (int64_t)dgq_sm_count() * 2);
+  const bool use_tensor = dgq_use_tensor_gemm();
   for (int i1 = 0; i1 < K; i1 += blocksize) {
     a.i1 = i1;
     a.bw = std::min(blocksize, K - i1);
@@ -390,9 +393,21 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
     }
     const int i2 = i1 + a.bw;
     if (i2 < K) {
-      GemmArgs g = gemm_args(a.err, MAX_BLOCK, 1, U + (int64_t)i1 * ldu + i2, ldu, 1,
-                             W + i2, ldw, 1, N_out, K - i2, a.bw, -1.f, 1.f);
-      launch_gemm(g, st);
+      bool done = false;
+      if (use_tensor && a.bw == MAX_BLOCK && N_out >= dgq::TGEMM_TILE) {
+        dgq::TGemmArgs t = {};
+        t.a = a.err; t.lda = MAX_BLOCK;
+        t.b = U + (int64_t)i1 * ldu + i2; t.ldb = ldu; t.b_is_kn = 1;
+        t.c = W + i2; t.ldc = ldw;
+        t.m = N_out; t.n = K - i2; t.k = a.bw; t.alpha = -1.f; t.beta = 1.f;
+        t.info = nullptr;
+        done = dgq::tgemm_supported(t) && dgq::tgemm_launch(t, st);
+      }
+      if (!done) {
+        GemmArgs g = gemm_args(a.err, MAX_BLOCK, 1, U + (int64_t)i1 * ldu + i2, ldu, 1,
+                               W + i2, ldw, 1, N_out, K - i2, a.bw, -1.f, 1.f);
+        launch_gemm(g, st);
+      }
     }
   }
   return dgq_launch_status(dgq_cdiv(K, blocksize));

@@ -1,0 +1,369 @@
+// fp32-accurate matrix product on the sm_100a tensor cores:  C = alpha * A * B + beta * C.
+//
+// Data path per 32-wide reduction slice: TMA brings the fp32 tiles of A (128 x 32) and of
+// B (128 x 32, or 32 x 128 as four 32 x 32 panels) into 128-byte-swizzled shared memory;
+// four converter warps split every element x into hi = tf32(x) (round to nearest) and
+// lo = x - hi, writing hi in place and lo into a twin buffer at the same (swizzled)
+// offset; one thread then issues, per 8 reduction steps, three tcgen05.mma kind::tf32
+// instructions (hi*hi, hi*lo, lo*hi) into a 128 x 128 fp32 accumulator in tensor memory.
+// Accumulators are double buffered so that the epilogue warps (TMEM -> registers ->
+// alpha/beta update -> global) overlap the next tile's main loop.  CTAs are persistent
+// over the output tiles.
+//
+// Warps: 0 TMA producer (+ TMEM allocation), 1 MMA issuer, 2-5 converters, 6-9 epilogue.
+// Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, reports
+// DGQ_INFO_WAIT_TIMEOUT, waits for copies in flight, frees its tensor memory and returns.
+#include <algorithm>
+
+#include "common.cuh"
+#include "tc05.cuh"
+#include "tgemm.cuh"
+
+namespace {
+
+constexpr int TILE = dgq::TGEMM_TILE;   // 128 x 128 output tile
+constexpr int BK = 32;                  // fp32 elements per slice = one 128-byte swizzle row
+constexpr int OPERAND_BYTES = TILE * BK * 4;       // 16 KB
+constexpr int STAGE_BYTES = 4 * OPERAND_BYTES;     // A hi, A lo, B hi, B lo
+constexpr int STAGES = 3;
+constexpr int THREADS = 320;
+constexpr uint32_t TMEM_COLS = 256;                // two 128-column accumulators
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+
+struct Control {
+  uint64_t full[STAGES], conv[STAGES], empty[STAGES];
+  uint64_t tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+struct Params {
+  float* c; int64_t ldc;
+  int m, n, k;
+  float alpha, beta;
+  int b_is_kn, lo_from_j, hi_from_j, hi_from_i, lower_only;
+  int tiles_m, tiles_n, n_tiles;
+  int32_t* info;
+};
+
+struct TileWork { int ti, tj, k_lo, n_slices; };
+
+__device__ __forceinline__ TileWork decode_tile(const Params& p, int t) {
+  TileWork w;
+  if (p.lower_only) {
+    // row ti holds min(ti + 1, tiles_n) tiles
+    int ti = 0, rem = t;
+    while (true) {
+      int in_row = min(ti + 1, p.tiles_n);
+      if (rem < in_row) break;
+      rem -= in_row;
+      ++ti;
+    }
+    w.ti = ti; w.tj = rem;
+  } else {
+    w.ti = t / p.tiles_n;
+    w.tj = t - w.ti * p.tiles_n;
+  }
+  w.k_lo = p.lo_from_j ? w.tj * TILE : 0;
+  int k_hi = p.k;
+  if (p.hi_from_j) k_hi = min(k_hi, w.tj * TILE + TILE);
+  else if (p.hi_from_i) k_hi = min(k_hi, w.ti * TILE + TILE);
+  w.n_slices = max(1, (k_hi - w.k_lo + BK - 1) / BK);
+  return w;
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+             const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* stages = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  Control* ctl = reinterpret_cast<Control*>(stages + (size_t)STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &ctl->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc05::mbar_init(&ctl->full[s], 1);
+      tc05::mbar_init(&ctl->conv[s], 4);
+      tc05::mbar_init(&ctl->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc05::mbar_init(&ctl->tmem_full[b], 1);
+      tc05::mbar_init(&ctl->tmem_empty[b], 4);
+    }
+    ctl->abort = 0;
+    tc05::fence_mbar_init();
+    tc05::prefetch_tensormap(&map_a);
+    tc05::prefetch_tensormap(&map_b);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tc05::tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tc05::tmem_relinquish();
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+        const TileWork w = decode_tile(p, t);
+        for (int s_ = 0; s_ < w.n_slices; ++s_, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!tc05::mbar_wait_bounded(&ctl->empty[s], ph ^ 1, abort_flag)) {
+            if (p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 11; }
+            ok = false;
+            break;
+          }
+          uint8_t* a_hi = stages + (size_t)s * STAGE_BYTES;
+          uint8_t* b_hi = a_hi + 2 * OPERAND_BYTES;
+          const int k0 = w.k_lo + s_ * BK;
+          tc05::mbar_expect_tx(&ctl->full[s], 2 * OPERAND_BYTES);
+          tc05::tma_load_2d(a_hi, &map_a, k0, w.ti * TILE, &ctl->full[s]);
+          if (!p.b_is_kn) {
+            tc05::tma_load_2d(b_hi, &map_b, k0, w.tj * TILE, &ctl->full[s]);
+          } else {
+#pragma unroll
+            for (int pn = 0; pn < TILE / 32; ++pn)
+              tc05::tma_load_2d(b_hi + pn * (32 * 128), &map_b, w.tj * TILE + pn * 32, k0,
+                                &ctl->full[s]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_nt = tc05::make_instr_desc(tc05::FMT_TF32, false, false, TILE, TILE);
+      const uint32_t idesc_nn = tc05::make_instr_desc(tc05::FMT_TF32, false, true, TILE, TILE);
+      const uint32_t idesc = p.b_is_kn ? idesc_nn : idesc_nt;
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++lt) {
+        const TileWork w = decode_tile(p, t);
+        const uint32_t ab = lt & 1, aph = (lt >> 1) & 1;
+        if (!tc05::mbar_wait_bounded(&ctl->tmem_empty[ab], aph ^ 1, abort_flag)) {
+          if (p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 12; }
+          break;
+        }
+        tc05::fence_after_sync();
+        const uint32_t acc = tmem_base + ab * TILE;
+        for (int s_ = 0; s_ < w.n_slices; ++s_, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!tc05::mbar_wait_bounded(&ctl->conv[s], ph, abort_flag)) {
+            if (p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 13; }
+            ok = false;
+            break;
+          }
+          tc05::fence_after_sync();
+          const uint32_t a_hi = tc05::smem_u32(stages + (size_t)s * STAGE_BYTES);
+          const uint32_t a_lo = a_hi + OPERAND_BYTES;
+          const uint32_t b_hi = a_hi + 2 * OPERAND_BYTES;
+          const uint32_t b_lo = a_hi + 3 * OPERAND_BYTES;
+#pragma unroll
+          for (int k8 = 0; k8 < BK / 8; ++k8) {
+            // A (and B in NT form): rows of 128 bytes along k -> step 8 floats = 32 bytes
+            // B in NN form: four panels of 32 k-rows x 128 bytes -> step 8 rows = 1024 bytes
+            const uint32_t a_off = k8 * 32;
+            const uint32_t b_off = p.b_is_kn ? k8 * 1024 : k8 * 32;
+            const uint32_t b_lbo = p.b_is_kn ? 32 * 128 : 0;
+            const uint64_t da_hi = tc05::make_smem_desc(a_hi + a_off, 0, 1024);
+            const uint64_t da_lo = tc05::make_smem_desc(a_lo + a_off, 0, 1024);
+            const uint64_t db_hi = tc05::make_smem_desc(b_hi + b_off, b_lbo, 1024);
+            const uint64_t db_lo = tc05::make_smem_desc(b_lo + b_off, b_lbo, 1024);
+            tc05::umma_tf32(acc, da_lo, db_hi, idesc, (s_ | k8) != 0 ? 1u : 0u);
+            tc05::umma_tf32(acc, da_hi, db_lo, idesc, 1u);
+            tc05::umma_tf32(acc, da_hi, db_hi, idesc, 1u);
+          }
+          tc05::umma_commit(&ctl->empty[s]);
+        }
+        if (ok) tc05::umma_commit(&ctl->tmem_full[ab]);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ hi/lo converters
+    const int ct = threadIdx.x - 64;  // 0..127
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+      const TileWork w = decode_tile(p, t);
+      for (int s_ = 0; s_ < w.n_slices; ++s_, ++it) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+        const bool got = tc05::mbar_wait_bounded(&ctl->full[s], ph, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0 && p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 14; }
+          ok = false;
+          break;
+        }
+        float4* hi_a = reinterpret_cast<float4*>(stages + (size_t)s * STAGE_BYTES);
+        float4* lo_a = hi_a + OPERAND_BYTES / 16;
+        float4* hi_b = hi_a + 2 * (OPERAND_BYTES / 16);
+        float4* lo_b = hi_a + 3 * (OPERAND_BYTES / 16);
+#pragma unroll
+        for (int r = 0; r < OPERAND_BYTES / 16 / 128; ++r) {
+          const int idx = ct + r * 128;
+          const float4 xa = hi_a[idx], xb = hi_b[idx];
+          float4 ha, la, hb, lb;
+          ha.x = to_tf32(xa.x); ha.y = to_tf32(xa.y); ha.z = to_tf32(xa.z); ha.w = to_tf32(xa.w);
+          la.x = xa.x - ha.x; la.y = xa.y - ha.y; la.z = xa.z - ha.z; la.w = xa.w - ha.w;
+          hb.x = to_tf32(xb.x); hb.y = to_tf32(xb.y); hb.z = to_tf32(xb.z); hb.w = to_tf32(xb.w);
+          lb.x = xb.x - hb.x; lb.y = xb.y - hb.y; lb.z = xb.z - hb.z; lb.w = xb.w - hb.w;
+          hi_a[idx] = ha; lo_a[idx] = la; hi_b[idx] = hb; lo_b[idx] = lb;
+        }
+        // make the generic-proxy writes visible to the tensor core's (async proxy) reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) tc05::mbar_arrive(&ctl->conv[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    uint32_t lt = 0;
+    for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++lt) {
+      const TileWork w = decode_tile(p, t);
+      const uint32_t ab = lt & 1, aph = (lt >> 1) & 1;
+      const bool got = tc05::mbar_wait_bounded(&ctl->tmem_full[ab], aph, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0 && p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 15; }
+        break;
+      }
+      tc05::fence_after_sync();
+      const int row = w.ti * TILE + q * 32 + lane;
+      float* crow = p.c + (int64_t)row * p.ldc;
+#pragma unroll 1
+      for (int chunk = 0; chunk < TILE / 32; ++chunk) {
+        uint32_t v[32];
+        tc05::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE + chunk * 32, v);
+        tc05::tmem_ld_wait();
+        const int c0 = w.tj * TILE + chunk * 32;
+        if (row >= p.m || c0 >= p.n) continue;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const int c = c0 + j;
+          if (c >= p.n) break;
+          if (p.lower_only && c > row) break;
+          float o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = p.alpha * __uint_as_float(v[j + e]);
+          const bool full4 = (c + 3 < p.n) && (!p.lower_only || c + 3 <= row);
+          if (full4) {
+            float4* dst = reinterpret_cast<float4*>(crow + c);
+            if (p.beta != 0.f) {
+              const float4 old = *dst;
+              o[0] += p.beta * old.x; o[1] += p.beta * old.y;
+              o[2] += p.beta * old.z; o[3] += p.beta * old.w;
+            }
+            *dst = make_float4(o[0], o[1], o[2], o[3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (c + e < p.n && (!p.lower_only || c + e <= row)) {
+                float val = o[e];
+                if (p.beta != 0.f) val += p.beta * crow[c + e];
+                crow[c + e] = val;
+              }
+            }
+          }
+        }
+      }
+      tc05::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc05::mbar_arrive(&ctl->tmem_empty[ab]);
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) {
+    tc05::fence_after_sync();
+    tc05::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+namespace dgq {
+
+bool tgemm_supported(const TGemmArgs& g) {
+  if (g.m <= 0 || g.n <= 0 || g.k <= 0) return false;
+  if (!dgq_aligned(g.a, 16) || !dgq_aligned(g.b, 16) || !dgq_aligned(g.c, 16)) return false;
+  if (g.lda % 4 || g.ldb % 4 || g.ldc % 4) return false;
+  if (g.lo_from_j && (int64_t)(dgq_cdiv(g.n, TILE) - 1) * TILE >= g.k) return false;
+  return true;
+}
+
+bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(tgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)SMEM_BYTES) != cudaSuccess)
+      return false;
+    attr_set = true;
+  }
+  CUtensorMap map_a, map_b;
+  if (!tc05::make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.a, (uint64_t)g.m,
+                                (uint64_t)g.k, (uint64_t)g.lda * 4, TILE, BK))
+    return false;
+  const bool ok_b = g.b_is_kn
+      ? tc05::make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.b, (uint64_t)g.k,
+                                 (uint64_t)g.n, (uint64_t)g.ldb * 4, BK, 32)
+      : tc05::make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.b, (uint64_t)g.n,
+                                 (uint64_t)g.k, (uint64_t)g.ldb * 4, TILE, BK);
+  if (!ok_b) return false;
+  Params p;
+  p.c = g.c; p.ldc = g.ldc; p.m = g.m; p.n = g.n; p.k = g.k;
+  p.alpha = g.alpha; p.beta = g.beta;
+  p.b_is_kn = g.b_is_kn; p.lo_from_j = g.lo_from_j; p.hi_from_j = g.hi_from_j;
+  p.hi_from_i = g.hi_from_i; p.lower_only = g.lower_only;
+  p.tiles_m = (int)dgq_cdiv(g.m, TILE);
+  p.tiles_n = (int)dgq_cdiv(g.n, TILE);
+  if (g.lower_only) {
+    int64_t cnt = 0;
+    for (int ti = 0; ti < p.tiles_m; ++ti) cnt += std::min(ti + 1, p.tiles_n);
+    p.n_tiles = (int)cnt;
+  } else {
+    p.n_tiles = p.tiles_m * p.tiles_n;
+  }
+  p.info = g.info;
+  const unsigned grid = (unsigned)std::min(p.n_tiles, dgq_sm_count());
+  tgemm_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+  dgq_note_launches(1);
+  return cudaGetLastError() == cudaSuccess;
+}
+
+}  // namespace dgq
+
+// ---- C ABI ---------------------------------------------------------------------------------
+DGQ_EXPORT int32_t dgq_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb,
+                                int32_t b_is_kn, float* c, int64_t ldc, int32_t m, int32_t n,
+                                int32_t k, float alpha, float beta, int32_t lower_only,
+                                int32_t* info, void* stream) {
+  DGQ_REQUIRE(a && b && c && m > 0 && n > 0 && k > 0, DGQ_ERR_ARG);
+  DGQ_REQUIRE(lda >= k && ldc >= n && ldb >= (b_is_kn ? n : k), DGQ_ERR_ARG);
+  int32_t arch = dgq_device_check();
+  if (arch != DGQ_OK) return arch;
+  dgq::TGemmArgs t = {};
+  t.a = a; t.lda = lda; t.b = b; t.ldb = ldb; t.c = c; t.ldc = ldc;
+  t.m = m; t.n = n; t.k = k; t.alpha = alpha; t.beta = beta;
+  t.b_is_kn = b_is_kn ? 1 : 0; t.lower_only = lower_only ? 1 : 0; t.info = info;
+  DGQ_REQUIRE(dgq::tgemm_supported(t), DGQ_ERR_ALIGN);
+  return dgq::tgemm_launch(t, dgq_stream(stream)) ? DGQ_OK : DGQ_ERR_LAUNCH;
+}

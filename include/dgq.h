@@ -123,6 +123,22 @@ int64_t dgq_inv_chol_workspace_bytes(int32_t K);
 int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t* info,
                            void* ws, int64_t ws_bytes, void* stream);
 
+/* ---- fp32-accurate matrix product on the tensor cores -------------------------
+ * The product behind the inverse factor and the trailing update
+ * (`W_block[:, j+1:] -= err @ H_inv[j, j+1:]` batched over a block, core/gptq.py:187,
+ * and the products inside torch.cholesky_inverse, core/gptq.py:122), exported so that it
+ * can be checked on its own.
+ *
+ * C(m,n) = alpha * A(m,k) * B + beta * C, all fp32 row-major.  B is (n,k) when
+ * b_is_kn == 0 (C = A * B^T) and (k,n) otherwise.  Operands are split into tf32 high
+ * and low parts and three tcgen05 products are accumulated, so results agree with an
+ * fp32 product to about 1e-6 relative.  lower_only != 0 computes and writes only
+ * entries with column <= row.  Bases 16-byte aligned, leading dimensions multiples of 4.
+ */
+int32_t dgq_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb, int32_t b_is_kn,
+                     float* c, int64_t ldc, int32_t m, int32_t n, int32_t k,
+                     float alpha, float beta, int32_t lower_only, int32_t* info, void* stream);
+
 /* ---- blockwise quantization -----------------------------------------------
  * Replaces the block/column loop of GPTQ.quantize, core/gptq.py:131-194, with the
  * scale/zero formula of :165-169 and the quantize/dequantize formula of :175,179.

@@ -1,0 +1,121 @@
+"""Host-side logic of the multi-GPU path on CPU: sharding, owner placement and the Hessian
+exchange over a world_size-2 gloo group."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from distributed_gptq_b200.coordinator import (DistributedConfig, DistributedGPTQCoordinator,
+                                               QuantizationMode, assign_owners,
+                                               create_distributed_config, layer_cost, shard_indices)
+from distributed_gptq_b200.quantizer import QuantizationConfig, calibration_samples
+
+
+def test_shard_indices_partition():
+    for n in (0, 1, 7, 128, 129):
+        for w in (1, 2, 3, 8):
+            parts = [shard_indices(n, r, w) for r in range(w)]
+            flat = sorted(i for p in parts for i in p)
+            assert flat == list(range(n))                       # every sequence exactly once
+            assert max(len(p) for p in parts) - min(len(p) for p in parts) <= 1
+            assert parts[0][:3] == list(range(0, n, w))[:3]     # rank r takes r, r+W, ...
+
+
+def test_assign_owners_is_deterministic_and_balanced():
+    # one Llama-7B decoder block: q,k,v,o (4096x4096), gate/up (11008x4096), down (4096x11008)
+    shapes = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
+    costs = [layer_cost(o, i) for o, i in shapes] * 32
+    for w in (1, 2, 4, 8):
+        own = assign_owners(costs, w)
+        assert own == assign_owners(list(costs), w)
+        assert set(own) <= set(range(w))
+        load = [sum(c for c, o in zip(costs, own) if o == r) for r in range(w)]
+        assert max(load) <= 1.05 * (sum(costs) / w)
+    assert assign_owners([5.0, 1.0, 1.0], 2) == [0, 1, 1]
+
+
+def test_config_surface(monkeypatch):
+    c = QuantizationConfig()
+    assert (c.bits, c.group_size, c.actorder, c.percdamp, c.blocksize, c.calibration_samples,
+            c.use_triton, c.save_packed) == (4, 128, False, 0.01, 128, 128, False, True)
+    c.validate()
+    QuantizationConfig(bits=8, group_size=-1).validate()
+    for bad in (dict(bits=5), dict(group_size=0), dict(percdamp=1.5)):
+        with pytest.raises(AssertionError):
+            QuantizationConfig(**bad).validate()
+    for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    d = create_distributed_config()
+    assert d.mode == QuantizationMode.SINGLE_GPU and d.world_size == 1 and d.is_main_process
+    assert d.master_port == "12355" and d.backend == "nccl" and d.init_timeout == 1800
+    monkeypatch.setenv("WORLD_SIZE", "4")
+    monkeypatch.setenv("RANK", "2")
+    d = create_distributed_config()
+    assert d.mode == QuantizationMode.DATA_PARALLEL and d.is_distributed and not d.is_main_process
+    assert create_distributed_config("model_parallel").mode == QuantizationMode.MODEL_PARALLEL
+
+
+def test_calibration_sample_normalisation():
+    assert len(calibration_samples([torch.zeros(2, 5), torch.zeros(3, 5)], 128)) == 5
+    assert len(calibration_samples(torch.zeros(7, 5), 4)) == 4
+    s = calibration_samples([{"input_ids": torch.zeros(2, 5, dtype=torch.long), "use_cache": False}], 9)
+    assert len(s) == 2 and s[0]["input_ids"].shape == (1, 5) and s[0]["use_cache"] is False
+    loader = torch.utils.data.DataLoader(torch.utils.data.TensorDataset(torch.zeros(6, 3)), batch_size=4)
+    assert len(calibration_samples(loader, 128)) == 6
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, mode, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        cfg = DistributedConfig(mode=QuantizationMode.DATA_PARALLEL, world_size=world, rank=rank,
+                                local_rank=0, master_addr="127.0.0.1", master_port=str(port),
+                                backend="gloo", init_timeout=60, hessian_exchange=mode)
+        co = DistributedGPTQCoordinator(cfg)
+        co.device = torch.device("cpu")
+        with co.distributed_context():
+            assert dist.get_world_size() == world
+            hs = {"a": torch.full((4, 4), float(rank + 1)), "b": torch.full((2, 2), 10.0 * (rank + 1))}
+            owners = {"a": 0, "b": 1}
+            co.exchange_hessians(hs, owners)
+            total_a, total_b = float(sum(range(1, world + 1))), 10.0 * sum(range(1, world + 1))
+            if mode == "all_reduce" or rank == 0:
+                assert torch.all(hs["a"] == total_a)
+            if mode == "all_reduce" or rank == 1:
+                assert torch.all(hs["b"] == total_b)
+            t = torch.tensor([float(rank)])
+            co.comm.broadcast_tensor(t, src=1)
+            assert float(t) == 1.0
+            t = torch.tensor([1.0])
+            co.comm.all_reduce_tensor(t)
+            assert float(t) == world
+            assert co.comm.broadcast_object({"x": rank}, src=0) == {"x": 0}
+            shard = co.shard_calibration(list(range(7)))
+            assert shard == list(range(rank, 7, world))
+            co.comm.barrier()
+        assert not dist.is_initialized()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, f"{type(e).__name__}: {e}"))
+
+
+@pytest.mark.parametrize("mode", ["owner", "all_reduce"])
+def test_exchange_over_gloo(mode):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
