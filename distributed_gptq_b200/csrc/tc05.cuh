@@ -149,11 +149,17 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // For a K-major 128-byte-swizzled operand (rows of 128 bytes run along K):
 //   stride byte offset = distance between groups of 8 rows (along M/N); the leading
 //   offset is not used when the K extent of one instruction stays inside one row.
+// 32-bit operands whose contiguous dimension is M or N must use the 128-byte swizzle
+// with 32-byte atoms (layout code 1; TMA mode SWIZZLE_128B_ATOM_32B): 32-byte pieces of a
+// 128-byte row are permuted with a period of 4 rows, so groups along K are 4 rows
+// (512 bytes when packed) apart.
 constexpr uint64_t SWIZZLE_128B = 2;
+constexpr uint64_t SWIZZLE_128B_BASE32B = 1;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes,
+                                                   uint64_t layout = SWIZZLE_128B) {
   return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (SWIZZLE_128B << 61);
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (layout << 61);
 }
 
 // Instruction descriptor (32-bit) for kind::f16 / kind::tf32:
@@ -227,10 +233,11 @@ inline PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 }
 
 // 2-D row-major tensor (rows, cols) with `ld_bytes` between rows; box = (box_rows,
-// box_cols) with box_cols * elem_bytes == 128 and the 128-byte swizzle.
+// box_cols) with box_cols * elem_bytes == 128 and a 128-byte swizzle mode.
 inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes,
                                const void* base, uint64_t rows, uint64_t cols, uint64_t ld_bytes,
-                               uint32_t box_rows, uint32_t box_cols) {
+                               uint32_t box_rows, uint32_t box_cols,
+                               CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   auto enc = tensor_map_encoder();
   if (!enc) return false;
   cuuint64_t dims[2] = {cols, rows};
@@ -239,7 +246,7 @@ inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint
   cuuint32_t estr[2] = {1, 1};
   (void)elem_bytes;
   return enc(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 }  // namespace tc05

@@ -1,7 +1,8 @@
 // fp32-accurate matrix product on the sm_100a tensor cores:  C = alpha * A * B + beta * C.
 //
 // Data path per 32-wide reduction slice: TMA brings the fp32 tiles of A (128 x 32) and of
-// B (128 x 32, or 32 x 128 as four 32 x 32 panels) into 128-byte-swizzled shared memory;
+// B (128 x 32, or 32 x 128 as four 32 x 32 panels) into 128-byte-swizzled shared memory
+// (32-byte swizzle atoms for the n-contiguous form of B, as tf32 operands require);
 // four converter warps split every element x into hi = tf32(x) (round to nearest) and
 // lo = x - hi, writing hi in place and lo into a twin buffer at the same (swizzled)
 // offset; one thread then issues, per 8 reduction steps, three tcgen05.mma kind::tf32
@@ -179,11 +180,14 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             // B in NN form: four panels of 32 k-rows x 128 bytes -> step 8 rows = 1024 bytes
             const uint32_t a_off = k8 * 32;
             const uint32_t b_off = p.b_is_kn ? k8 * 1024 : k8 * 32;
+            // (n-contiguous fp32 uses the 32-byte-atom swizzle: groups of 4 k-rows, 512 bytes apart)
             const uint32_t b_lbo = p.b_is_kn ? 32 * 128 : 0;
+            const uint32_t b_sbo = p.b_is_kn ? 512 : 1024;
+            const uint64_t b_layout = p.b_is_kn ? tc05::SWIZZLE_128B_BASE32B : tc05::SWIZZLE_128B;
             const uint64_t da_hi = tc05::make_smem_desc(a_hi + a_off, 0, 1024);
             const uint64_t da_lo = tc05::make_smem_desc(a_lo + a_off, 0, 1024);
-            const uint64_t db_hi = tc05::make_smem_desc(b_hi + b_off, b_lbo, 1024);
-            const uint64_t db_lo = tc05::make_smem_desc(b_lo + b_off, b_lbo, 1024);
+            const uint64_t db_hi = tc05::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_layout);
+            const uint64_t db_lo = tc05::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_layout);
             tc05::umma_tf32(acc, da_lo, db_hi, idesc, (s_ | k8) != 0 ? 1u : 0u);
             tc05::umma_tf32(acc, da_hi, db_lo, idesc, 1u);
             tc05::umma_tf32(acc, da_hi, db_hi, idesc, 1u);
@@ -324,7 +328,8 @@ bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
     return false;
   const bool ok_b = g.b_is_kn
       ? tc05::make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.b, (uint64_t)g.k,
-                                 (uint64_t)g.n, (uint64_t)g.ldb * 4, BK, 32)
+                                 (uint64_t)g.n, (uint64_t)g.ldb * 4, BK, 32,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)
       : tc05::make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.b, (uint64_t)g.n,
                                  (uint64_t)g.k, (uint64_t)g.ldb * 4, TILE, BK);
   if (!ok_b) return false;
