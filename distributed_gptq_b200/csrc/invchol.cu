@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(NB)
 leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
   __shared__ float S[NB][NB + 1];
   __shared__ float X[NB][NB + 1];
+  __shared__ float colk[2][NB];   // column k of L, double buffered: one barrier per step less
   const int t = threadIdx.x;
   for (int idx = t; idx < NB * NB; idx += NB) {
     const int i = idx / NB, j = idx % NB;
@@ -92,23 +93,36 @@ leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, 
       lik = (t == k) ? r : __fdiv_rn(S[t][k], r);
       S[t][k] = lik;
     }
+    float* ck = colk[k & 1];
+    ck[t] = lik;
     __syncthreads();
     if (t > k) {
-#pragma unroll 4
-      for (int j = k + 1; j <= t; ++j) S[t][j] = fmaf(-lik, S[j][k], S[t][j]);
+      // row t of the trailing block, eight entries at a time: all loads of a batch are
+      // issued before its stores so their latencies overlap
+      int j = k + 1;
+      for (; j + 7 <= t; j += 8) {
+        float c[8], v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { c[u] = ck[j + u]; v[u] = S[t][j + u]; }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) S[t][j + u] = fmaf(-lik, c[u], v[u]);
+      }
+      for (; j <= t; ++j) S[t][j] = fmaf(-lik, ck[j], S[t][j]);
     }
-    __syncthreads();
+    __syncthreads();  // the next step's pivot S[k+1][k+1] was just written by thread k+1
   }
   // X = L^-1, column t; entries above the diagonal come out as exact zeros
   for (int i = 0; i < NB; ++i) {
-    float acc0 = (i == t) ? 1.f : 0.f, acc1 = 0.f;
+    float a0 = (i == t) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     int k = 0;
-    for (; k + 1 < i; k += 2) {
-      acc0 = fmaf(-S[i][k], X[k][t], acc0);
-      acc1 = fmaf(-S[i][k + 1], X[k + 1][t], acc1);
+    for (; k + 3 < i; k += 4) {
+      a0 = fmaf(-S[i][k], X[k][t], a0);
+      a1 = fmaf(-S[i][k + 1], X[k + 1][t], a1);
+      a2 = fmaf(-S[i][k + 2], X[k + 2][t], a2);
+      a3 = fmaf(-S[i][k + 3], X[k + 3][t], a3);
     }
-    if (k < i) acc0 = fmaf(-S[i][k], X[k][t], acc0);
-    X[i][t] = (i >= t) ? __fdiv_rn(acc0 + acc1, S[i][i]) : 0.f;
+    for (; k < i; ++k) a0 = fmaf(-S[i][k], X[k][t], a0);
+    X[i][t] = (i >= t) ? __fdiv_rn((a0 + a1) + (a2 + a3), S[i][i]) : 0.f;
   }
   __syncthreads();
   for (int idx = t; idx < NB * NB; idx += NB) {
