@@ -45,6 +45,9 @@ SIGNATURES = {
     "dgq_gptq_quantize_workspace_bytes": (_I64, [_I32, _I32, _I32]),
     "dgq_gptq_quantize": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _P, _I64,
                                  _P, _P, _P, _P, _I64, _P]),
+    "dgq_gptq_quantize_noalloc_max_rows": (_I32, []),
+    "dgq_gptq_quantize_noalloc": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _P, _I64,
+                                         _P, _P, _P, _P]),
     "dgq_find_params": (_I32, [_P, _I64, _I32, _I32, _I32, _P, _P, _P]),
     "dgq_quantize_rows": (_I32, [_P, _I64, _I32, _I32, _I32, _P, _P, _P, _I64, _P, _I64, _P]),
     "dgq_packed_row_bytes": (_I64, [_I32, _I32, _I32]),

@@ -412,3 +412,38 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   }
   return dgq_launch_status(dgq_cdiv(K, blocksize));
 }
+
+// ---- variant for callers that cannot allocate ---------------------------------------------------
+// Scratch for dgq_gptq_quantize_noalloc: the (rows x 128) buffer of scaled errors that the
+// block kernel hands to the trailing update.  It lives in the library's device image, so
+// every GPU that loads the library holds these 8 MiB until the process exits.
+constexpr int NOALLOC_MAX_ROWS = 16384;
+static __device__ __align__(256) float g_noalloc_err[(size_t)NOALLOC_MAX_ROWS * MAX_BLOCK];
+
+DGQ_EXPORT int32_t dgq_gptq_quantize_noalloc_max_rows(void) { return NOALLOC_MAX_ROWS; }
+
+DGQ_EXPORT int32_t dgq_gptq_quantize_noalloc(float* W, int64_t ldw, const float* U, int64_t ldu,
+                                             int32_t N_out, int32_t K, int32_t bits,
+                                             int32_t group_size, int32_t blocksize, uint8_t* codes,
+                                             int64_t ldc, float* scales, float* zeros,
+                                             double* total_error, void* stream) {
+  DGQ_REQUIRE(N_out > 0, DGQ_ERR_ARG);
+  DGQ_REQUIRE(N_out <= NOALLOC_MAX_ROWS, DGQ_ERR_SIZE);
+  // In host code the array's name is only a handle: the device address has to be asked
+  // for, once per device, with that device current.
+  constexpr int MAX_DEVICES = 64;
+  static float* scratch_of_device[MAX_DEVICES] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return DGQ_ERR_LAUNCH;
+  if (scratch_of_device[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_err) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      return DGQ_ERR_LAUNCH;
+    }
+    scratch_of_device[dev] = static_cast<float*>(p);
+  }
+  return dgq_gptq_quantize(W, ldw, U, ldu, N_out, K, bits, group_size, blocksize, codes, ldc,
+                           scales, zeros, total_error, scratch_of_device[dev],
+                           (int64_t)sizeof(float) * NOALLOC_MAX_ROWS * MAX_BLOCK, stream);
+}

@@ -158,6 +158,28 @@ int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int64_t ldu,
                           float* scales, float* zeros, double* total_error,
                           void* ws, int64_t ws_bytes, void* stream);
 
+/* Same computation as dgq_gptq_quantize for callers that must not allocate device
+ * memory - code running inside another framework's memory plan, or under an allocator
+ * that forbids cudaMalloc while a model is resident - and so cannot provide the
+ * workspace.  It has no counterpart in the reference.  The scaled-error scratch lives in a
+ * fixed array inside the library's device image (8 MiB per GPU that loads the library,
+ * held until the process exits), which limits N_out to
+ * dgq_gptq_quantize_noalloc_max_rows() = 16384 rows; more rows are rejected with
+ * DGQ_ERR_SIZE.  The call makes no cudaMalloc/cudaFree and uses no allocating library
+ * routine.  The first call on a device looks up the array's device address (a host-side
+ * set-up step): make that first call before starting any stream capture.  All calls on
+ * a device share the one array, whose contents are whatever the last call left (every
+ * entry that is read is written first, so nothing needs clearing); two calls that
+ * overlap on the same GPU - different streams or threads - race on it and must be
+ * serialised by the caller.
+ */
+int32_t dgq_gptq_quantize_noalloc_max_rows(void);
+int32_t dgq_gptq_quantize_noalloc(float* W, int64_t ldw, const float* U, int64_t ldu,
+                                  int32_t N_out, int32_t K, int32_t bits, int32_t group_size,
+                                  int32_t blocksize, uint8_t* codes, int64_t ldc,
+                                  float* scales, float* zeros, double* total_error,
+                                  void* stream);
+
 /* ---- scale/zero and quantize on their own ("Quantizer.find_params/quantize") --
  * find_params: per row of x (rows, cols): scale = (max-min)/maxq (1 if zero),
  *   zero = round(-min/scale)                       (core/gptq.py:165-169)

@@ -1,0 +1,76 @@
+"""dgq_gptq_quantize_noalloc: the entry point for callers that cannot hand the library a
+workspace (they run under a memory plan or an allocator that does not let them call
+cudaMalloc).  It must produce exactly what dgq_gptq_quantize produces, call after call,
+although all calls share one scratch array inside the library.
+
+Collected last on purpose: a run that stops at the first failure has then already run
+every other test.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(N_out, K, seed):
+    from distributed_gptq_b200 import _C
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    X = torch.randn(4 * K, K, generator=g, device="cuda").to(torch.bfloat16)
+    H = torch.zeros((K, K), dtype=torch.float32, device="cuda")
+    _C.hessian_accum(X, H)
+    Hp, _ = _C.hessian_prepare(H, 0.5, 0.01, None)
+    U = _C.inv_chol_upper(Hp)
+    W = torch.randn(N_out, K, generator=g, device="cuda") * 0.02
+    return W, U
+
+
+def _call_noalloc(dgq, W, U, bits, group_size, blocksize):
+    N_out, K = W.shape
+    ng = 1 if group_size <= 0 or group_size >= K else -(-K // group_size)
+    codes = torch.empty((N_out, K), dtype=torch.uint8, device="cuda")
+    scales = torch.zeros((N_out, ng), dtype=torch.float32, device="cuda")
+    zeros = torch.zeros((N_out, ng), dtype=torch.float32, device="cuda")
+    terr = torch.zeros(1, dtype=torch.float64, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = dgq.lib().dgq_gptq_quantize_noalloc(p(W), W.stride(0), p(U), U.stride(0), N_out, K, bits,
+                                             group_size, blocksize, p(codes), K, p(scales), p(zeros),
+                                             p(terr), st)
+    return rc, codes, scales, zeros, terr
+
+
+@pytest.mark.parametrize("N_out,K,bits,g", [(300, 512, 4, 128), (64, 384, 3, 64)])
+def test_noalloc_matches_workspace_entry_point_twice(dgq, N_out, K, bits, g):
+    W0, U = _inputs(N_out, K, N_out + K)
+    Wref = W0.clone()
+    codes_ref, s_ref, z_ref, terr_ref = dgq.gptq_quantize(Wref, U, bits, g, 128)
+    for call in range(2):                      # the second call finds the first call's leftovers
+        W = W0.clone()
+        before = torch.cuda.memory_allocated()
+        rc, codes, s, z, terr = _call_noalloc(dgq, W, U, bits, g, 128)
+        assert rc == 0, dgq.status_string(rc)
+        torch.cuda.synchronize()
+        assert torch.equal(codes, codes_ref), f"call {call}"
+        assert torch.equal(W, Wref) and torch.equal(s, s_ref) and torch.equal(z, z_ref)
+        assert abs(float(terr) - float(terr_ref)) <= 1e-9 * abs(float(terr_ref))
+        # different shape in between, so that stale scratch contents would show
+        if call == 0:
+            W2, U2 = _inputs(96, 256, 7)
+            rc2, *_ = _call_noalloc(dgq, W2, U2, 4, 128, 128)
+            assert rc2 == 0
+        assert torch.cuda.memory_allocated() >= before   # the tensors above; nothing is freed behind torch
+
+
+def test_noalloc_rejects_too_many_rows(dgq):
+    L = dgq.lib()
+    max_rows = L.dgq_gptq_quantize_noalloc_max_rows()
+    assert max_rows == 16384
+    W = torch.zeros((8, 128), device="cuda")
+    U = torch.eye(128, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    dummy = torch.zeros(16, dtype=torch.float64, device="cuda")
+    rc = L.dgq_gptq_quantize_noalloc(p(W), 128, p(U), 128, max_rows + 1, 128, 4, 128, 128, p(dummy),
+                                     128, p(dummy), p(dummy), p(dummy), None)
+    assert rc == -7 and "maximum" in dgq.status_string(rc)
