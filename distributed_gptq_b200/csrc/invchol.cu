@@ -60,22 +60,29 @@ reverse_out_kernel(const float* __restrict__ V, int64_t ldv, float* __restrict__
 }
 
 // ---- leaf: Cholesky + inverse of one diagonal block ------------------------------------------
-// 64 threads, the block lives in shared memory.  D (nb x nb, nb <= 64, lower part read) is
-// replaced by inv(chol(D)) (lower; the part above the diagonal is written as zeros).
-// Factorisation: right-looking, thread t owns row t; per column one division by the
-// pivot's square root (every thread takes the root itself, so the pivot needs no
-// broadcast step) and a rank-1 update of the row's remaining entries.  Inverse:
-// thread t solves L x = e_t for column t by forward substitution; all threads walk the
-// same row of L at the same time (a broadcast read) against their own column of X.
-// The loops are ordinary loops: the code stays small enough to live in the instruction
-// cache, which matters for a kernel that sits on the critical path ~K/64 times.
-__global__ void __launch_bounds__(NB)
+// One CTA of 256 threads, the block lives in shared memory.  D (nb x nb, nb <= 64, lower
+// part read) is replaced by inv(chol(D)) (lower; the part above the diagonal is written as
+// zeros).  This kernel sits on the critical path K/64 times, so it is written for latency:
+//  * all 256 threads move the block in and out of shared memory;
+//  * factorisation, right-looking: row r = tid % 64 is shared by four threads that update
+//    every fourth entry of it; the pivot's reciprocal square root comes from rsqrt plus one
+//    Newton step (every thread computes it itself: no broadcast step), the column is
+//    broadcast through a double-buffered array so one barrier per step is enough for it;
+//  * inverse: thread t < 64 solves L x = e_t for column t by forward substitution, all
+//    threads walking the same row of L (a broadcast read) against their own column of X.
+// Loops are ordinary loops so that the code stays resident in the instruction cache.
+constexpr int LEAF_THREADS = 256;
+
+__global__ void __launch_bounds__(LEAF_THREADS)
 leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
   __shared__ float S[NB][NB + 1];
   __shared__ float X[NB][NB + 1];
-  __shared__ float colk[2][NB];   // column k of L, double buffered: one barrier per step less
-  const int t = threadIdx.x;
-  for (int idx = t; idx < NB * NB; idx += NB) {
+  __shared__ float colk[2][NB];
+  const int tid = threadIdx.x;
+  const int r = tid & (NB - 1);   // row owned during the factorisation
+  const int part = tid >> 6;      // which quarter of the row's entries
+#pragma unroll 4
+  for (int idx = tid; idx < NB * NB; idx += LEAF_THREADS) {
     const int i = idx / NB, j = idx % NB;
     S[i][j] = (i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f) : (i == j ? 1.f : 0.f);
   }
@@ -83,49 +90,52 @@ leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, 
   for (int k = 0; k < NB; ++k) {
     float d = S[k][k];
     if (!(d > 0.f) || !isfinite(d)) {
-      if (t == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
+      if (tid == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
         info[1] = pivot_base - k;
       d = 1.f;
     }
-    const float r = sqrtf(d);
-    float lik = 0.f;
-    if (t >= k) {
-      lik = (t == k) ? r : __fdiv_rn(S[t][k], r);
-      S[t][k] = lik;
-    }
+    float rs = rsqrtf(d);
+    rs = rs * fmaf(-0.5f * d * rs, rs, 1.5f);   // one Newton step: 1/sqrt(d) to ~1 ulp
+    const float lik = (r == k) ? d * rs : (r > k ? S[r][k] * rs : 0.f);
     float* ck = colk[k & 1];
-    ck[t] = lik;
+    if (part == 0) ck[r] = lik;
     __syncthreads();
-    if (t > k) {
-      // row t of the trailing block, eight entries at a time: all loads of a batch are
-      // issued before its stores so their latencies overlap
-      int j = k + 1;
-      for (; j + 7 <= t; j += 8) {
+    if (r > k) {
+      if (part == 0) S[r][k] = lik;
+      // entries j = k+1+part, k+5+part, ... <= r of row r, eight at a time with all loads
+      // of a batch issued before its stores
+      int j = k + 1 + part;
+      for (; j + 28 <= r; j += 32) {
         float c[8], v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { c[u] = ck[j + u]; v[u] = S[t][j + u]; }
+        for (int u = 0; u < 8; ++u) { c[u] = ck[j + 4 * u]; v[u] = S[r][j + 4 * u]; }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) S[t][j + u] = fmaf(-lik, c[u], v[u]);
+        for (int u = 0; u < 8; ++u) S[r][j + 4 * u] = fmaf(-lik, c[u], v[u]);
       }
-      for (; j <= t; ++j) S[t][j] = fmaf(-lik, ck[j], S[t][j]);
+      for (; j <= r; j += 4) S[r][j] = fmaf(-lik, ck[j], S[r][j]);
+    } else if (r == k && part == 0) {
+      S[r][k] = lik;
     }
-    __syncthreads();  // the next step's pivot S[k+1][k+1] was just written by thread k+1
+    __syncthreads();  // the next pivot S[k+1][k+1] and the column buffer's reuse two steps on
   }
   // X = L^-1, column t; entries above the diagonal come out as exact zeros
-  for (int i = 0; i < NB; ++i) {
-    float a0 = (i == t) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    int k = 0;
-    for (; k + 3 < i; k += 4) {
-      a0 = fmaf(-S[i][k], X[k][t], a0);
-      a1 = fmaf(-S[i][k + 1], X[k + 1][t], a1);
-      a2 = fmaf(-S[i][k + 2], X[k + 2][t], a2);
-      a3 = fmaf(-S[i][k + 3], X[k + 3][t], a3);
+  if (tid < NB) {
+    const int t = tid;
+    for (int i = 0; i < NB; ++i) {
+      float a0 = (i == t) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      int k = 0;
+      for (; k + 3 < i; k += 4) {
+        a0 = fmaf(-S[i][k], X[k][t], a0);
+        a1 = fmaf(-S[i][k + 1], X[k + 1][t], a1);
+        a2 = fmaf(-S[i][k + 2], X[k + 2][t], a2);
+        a3 = fmaf(-S[i][k + 3], X[k + 3][t], a3);
+      }
+      for (; k < i; ++k) a0 = fmaf(-S[i][k], X[k][t], a0);
+      X[i][t] = (i >= t) ? __fdiv_rn((a0 + a1) + (a2 + a3), S[i][i]) : 0.f;
     }
-    for (; k < i; ++k) a0 = fmaf(-S[i][k], X[k][t], a0);
-    X[i][t] = (i >= t) ? __fdiv_rn((a0 + a1) + (a2 + a3), S[i][i]) : 0.f;
   }
   __syncthreads();
-  for (int idx = t; idx < NB * NB; idx += NB) {
+  for (int idx = tid; idx < NB * NB; idx += LEAF_THREADS) {
     const int i = idx / NB, j = idx % NB;
     if (i < nb && j < nb) D[(int64_t)i * ldd + j] = X[i][j];
   }
@@ -180,7 +190,7 @@ void rec(Plan& p, int o, int n, int depth) {
   float* V = p.V;
   const int64_t ld = p.ldv;
   if (n <= NB) {
-    leaf_inv_chol_kernel<<<1, NB, 0, p.st>>>(V + (int64_t)o * ld + o, ld, n, p.info, p.K - 1 - o);
+    leaf_inv_chol_kernel<<<1, LEAF_THREADS, 0, p.st>>>(V + (int64_t)o * ld + o, ld, n, p.info, p.K - 1 - o);
     ++p.leaves;
     return;
   }
