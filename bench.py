@@ -300,6 +300,16 @@ def cpu_reference_sample(scale: float = 1.0):
 
 # ----------------------------------------------------------------------------- main
 def main():
+    # Libraries (NCCL's version banner, for one) may write to stdout; the JSON line must be
+    # the only thing there, so everything else is sent to stderr.
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = sys.stderr
+
+    def emit(obj):
+        real_stdout.write(json.dumps(obj) + "\n")
+        real_stdout.flush()
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -329,7 +339,7 @@ def main():
             if i >= args.warmup:
                 times.append(t)
         v = sum(times) / len(times)
-        print(json.dumps({
+        emit(({
             "impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": v * 1e3,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
@@ -437,7 +447,7 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             v, cores, sample = cpu_reference_sample()
             cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
-        print(json.dumps({
+        emit(({
             "metric": metric, "value": ms_step / 1e3, "unit": unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
