@@ -4,7 +4,7 @@
 //   1. gptq_block8_kernel - eight lanes per weight row, four rows per warp.  A lane
 //      keeps 16 columns of the 128-column block in registers (four float4 chunks,
 //      interleaved over the lanes so that shared-memory reads of the block of U are
-//      conflict free).  Columns are visited in order, the loop fully unrolled: the
+//      conflict free).  Columns are visited in order: the
 //      owning lane's value is broadcast inside its group of eight with a shuffle,
 //      every lane of the group evaluates the quantize/dequantize formulas on it (so
 //      the scaled error needs no second broadcast) and applies the error feedback
@@ -12,7 +12,9 @@
 //      leave through 16-byte stores.  (gptq_block_kernel, one warp per row, is the
 //      general variant for ragged blocks and groups narrower than 32 columns.)
 //   2. trailing update - W[:, i2:] -= Err * U[i1:i2, i2:], an fp32-accurate product on
-//      the tensor cores (tgemm.cu; on the CUDA cores for ragged or tiny shapes).
+//      the tensor cores (tgemm.cu; on the CUDA cores for ragged or tiny shapes), applied
+//      in two levels: at once to the rest of the current 512-column super-block, and once
+//      per super-block (reduction length 512) to all columns beyond it.
 //
 // Group scale/zero are taken from W as it stands when the group's first column is
 // reached by the block loop (all earlier blocks' trailing updates applied, none of
@@ -27,6 +29,7 @@
 namespace {
 
 constexpr int MAX_BLOCK = 128;
+constexpr int SUPER_BLOCK = 512;   // columns whose updates of far columns are applied together
 constexpr int ROWS_PER_CTA = 16;  // one warp each
 
 struct QuantArgs {
@@ -34,7 +37,8 @@ struct QuantArgs {
   const float* U; int64_t ldu;
   uint8_t* codes; int64_t ldc;
   float* scales; float* zeros; int n_groups;
-  float* err;            // (N_out, MAX_BLOCK)
+  float* err;            // (N_out, err_ld): scaled errors of the current super-block
+  int64_t err_ld; int err_off;  // row stride and first column of the current block in it
   double* total_error;
   int N_out, K, i1, bw;  // block start and width
   int group;             // effective group size (K for per-channel)
@@ -177,7 +181,7 @@ gptq_block_kernel(const QuantArgs a) {
       }
     }
     // ---- outputs
-    float* erow = a.err + (int64_t)row * MAX_BLOCK;
+    float* erow = a.err + (int64_t)row * a.err_ld + a.err_off;
     uint8_t* crow = a.codes + (int64_t)row * a.ldc + a.i1;
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
@@ -187,8 +191,6 @@ gptq_block_kernel(const QuantArgs a) {
         crow[c] = (uint8_t)code[t];
         erow[c] = ev[t];
         err_sq += (double)ev[t] * (double)ev[t];
-      } else {
-        erow[c] = 0.f;
       }
     }
   }
@@ -272,35 +274,43 @@ gptq_block8_kernel(const QuantArgs a) {
         }
       }
     }
-    // ---- the column loop, fully unrolled: every register index below is a constant
+    // ---- the column loop.  Columns are visited in order j = 32*ij + 4*owner + e.  The
+    // loops over ij (which of the lane's chunks) and e (element of the chunk) are unrolled
+    // so that every register index is a constant; the loop over the owning lane is a real
+    // loop, which keeps the code small enough to stay in the instruction cache.
 #pragma unroll
-    for (int j = 0; j < MAX_BLOCK; ++j) {
-      const int ij = j >> 5;            // which of the lane's four chunks holds column j
-      const int owner = (j >> 2) & 7;   // lane of the group that holds it
-      const int reg = 4 * ij + (j & 3);
-      const float wj = __shfl_sync(0xffffffffu, w[reg], owner, 8);
-      const float sj = sg[j / GW], zj = zg[j / GW];
-      const float q = dgq_quant_level(wj, sj, zj, a.maxq);
-      const float wh = dgq_dequant_level(q, sj, zj);
-      const float e = __fdiv_rn(__fsub_rn(wj, wh), Us[j * MAX_BLOCK + j]);
-      if (sub == owner) {
-        what[reg] = wh;
-        ev[reg] = e;
-        code[ij] |= ((uint32_t)q) << (8 * (j & 3));
-      }
-      // error feedback; U is zero left of the diagonal, so columns already done are untouched
+    for (int ij = 0; ij < 4; ++ij) {
+#pragma unroll 1
+      for (int owner = 0; owner < 8; ++owner) {
 #pragma unroll
-      for (int i = ij; i < 4; ++i) {
-        const float4 u = Us4[j * (MAX_BLOCK / 4) + sub + 8 * i];
-        w[4 * i + 0] = fmaf(-e, u.x, w[4 * i + 0]);
-        w[4 * i + 1] = fmaf(-e, u.y, w[4 * i + 1]);
-        w[4 * i + 2] = fmaf(-e, u.z, w[4 * i + 2]);
-        w[4 * i + 3] = fmaf(-e, u.w, w[4 * i + 3]);
+        for (int e4 = 0; e4 < 4; ++e4) {
+          const int j = 32 * ij + 4 * owner + e4;
+          const int reg = 4 * ij + e4;
+          const float wj = __shfl_sync(0xffffffffu, w[reg], owner, 8);
+          const float sj = sg[(32 * ij) / GW], zj = zg[(32 * ij) / GW];
+          const float q = dgq_quant_level(wj, sj, zj, a.maxq);
+          const float wh = dgq_dequant_level(q, sj, zj);
+          const float e = __fdiv_rn(__fsub_rn(wj, wh), Us[j * MAX_BLOCK + j]);
+          if (sub == owner) {
+            what[reg] = wh;
+            ev[reg] = e;
+            code[ij] |= ((uint32_t)q) << (8 * e4);
+          }
+          // error feedback; U is zero left of the diagonal, so columns already done are untouched
+#pragma unroll
+          for (int i = ij; i < 4; ++i) {
+            const float4 u = Us4[j * (MAX_BLOCK / 4) + sub + 8 * i];
+            w[4 * i + 0] = fmaf(-e, u.x, w[4 * i + 0]);
+            w[4 * i + 1] = fmaf(-e, u.y, w[4 * i + 1]);
+            w[4 * i + 2] = fmaf(-e, u.z, w[4 * i + 2]);
+            w[4 * i + 3] = fmaf(-e, u.w, w[4 * i + 3]);
+          }
+        }
       }
     }
     // ---- outputs
     if (live) {
-      float* erow = a.err + (int64_t)row * MAX_BLOCK;
+      float* erow = a.err + (int64_t)row * a.err_ld + a.err_off;
       uint8_t* crow = a.codes + (int64_t)row * a.ldc + a.i1;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -326,7 +336,9 @@ bool valid_bits(int b) { return b == 2 || b == 3 || b == 4 || b == 8; }
 
 DGQ_EXPORT int64_t dgq_gptq_quantize_workspace_bytes(int32_t N_out, int32_t K, int32_t blocksize) {
   if (N_out <= 0 || K <= 0 || blocksize <= 0 || blocksize > MAX_BLOCK) return DGQ_ERR_ARG;
-  return (int64_t)N_out * MAX_BLOCK * (int64_t)sizeof(float);
+  // room for the scaled errors of a whole super-block; a quarter of this (one block's
+  // worth) is the minimum dgq_gptq_quantize accepts, at the price of more trailing updates
+  return (int64_t)N_out * SUPER_BLOCK * (int64_t)sizeof(float);
 }
 
 DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int64_t ldu,
@@ -345,7 +357,7 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
     const bool multiple = group % blocksize == 0;
     DGQ_REQUIRE(divides || multiple, DGQ_ERR_UNSUPPORTED);
   }
-  DGQ_REQUIRE(ws_bytes >= dgq_gptq_quantize_workspace_bytes(N_out, K, blocksize), DGQ_ERR_WORKSPACE);
+  DGQ_REQUIRE(ws_bytes >= (int64_t)N_out * MAX_BLOCK * (int64_t)sizeof(float), DGQ_ERR_WORKSPACE);
   DGQ_REQUIRE(dgq_aligned(ws, 16), DGQ_ERR_ALIGN);
   cudaStream_t st = dgq_stream(stream);
 
@@ -379,36 +391,51 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   const unsigned grid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, ROWS_PER_CTA),
                                                     (int64_t)dgq_sm_count() * 2);
   const bool use_tensor = dgq_use_tensor_gemm();
-  for (int i1 = 0; i1 < K; i1 += blocksize) {
-    a.i1 = i1;
-    a.bw = std::min(blocksize, K - i1);
-    if (fast_layout && gpb != 0 && a.bw == MAX_BLOCK) {
-      const unsigned fgrid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, F_ROWS_PER_CTA),
-                                                         (int64_t)dgq_sm_count() * 3);
-      if (gpb == 1) gptq_block8_kernel<1><<<fgrid, F_WARPS * 32, smem, st>>>(a);
-      else if (gpb == 2) gptq_block8_kernel<2><<<fgrid, F_WARPS * 32, smem, st>>>(a);
-      else gptq_block8_kernel<4><<<fgrid, F_WARPS * 32, smem, st>>>(a);
-    } else {
-      gptq_block_kernel<<<grid, ROWS_PER_CTA * 32, (size_t)a.bw * MAX_BLOCK * sizeof(float), st>>>(a);
+  // Two-level lazy update: inside a super-block every block's errors update only the
+  // super-block's remaining columns; the columns beyond it receive one update per
+  // super-block with a reduction as long as the super-block is wide.  This cuts the
+  // read-modify-write traffic over W by the number of blocks per super-block.
+  int super_cols = (int)std::min<int64_t>(SUPER_BLOCK, ws_bytes / ((int64_t)N_out * sizeof(float)));
+  super_cols = std::max(MAX_BLOCK, super_cols / MAX_BLOCK * MAX_BLOCK);
+  super_cols = super_cols / blocksize * blocksize;  // block boundaries stay multiples of blocksize
+  a.err_ld = super_cols;
+  // W[:, c0:c1] -= Err[:, e0:e0+k] * U[r0:r0+k, c0:c1]
+  auto update = [&](int e0, int k, int r0, int c0, int c1) {
+    if (c1 <= c0 || k <= 0) return;
+    bool done = false;
+    if (use_tensor && k % 32 == 0 && e0 % 4 == 0 && N_out >= dgq::TGEMM_TILE) {
+      dgq::TGemmArgs t = {};
+      t.a = a.err + e0; t.lda = a.err_ld;
+      t.b = U + (int64_t)r0 * ldu + c0; t.ldb = ldu; t.b_is_kn = 1;
+      t.c = W + c0; t.ldc = ldw;
+      t.m = N_out; t.n = c1 - c0; t.k = k; t.alpha = -1.f; t.beta = 1.f;
+      t.info = nullptr;
+      done = dgq::tgemm_supported(t) && dgq::tgemm_launch(t, st);
     }
-    const int i2 = i1 + a.bw;
-    if (i2 < K) {
-      bool done = false;
-      if (use_tensor && a.bw == MAX_BLOCK && N_out >= dgq::TGEMM_TILE) {
-        dgq::TGemmArgs t = {};
-        t.a = a.err; t.lda = MAX_BLOCK;
-        t.b = U + (int64_t)i1 * ldu + i2; t.ldb = ldu; t.b_is_kn = 1;
-        t.c = W + i2; t.ldc = ldw;
-        t.m = N_out; t.n = K - i2; t.k = a.bw; t.alpha = -1.f; t.beta = 1.f;
-        t.info = nullptr;
-        done = dgq::tgemm_supported(t) && dgq::tgemm_launch(t, st);
-      }
-      if (!done) {
-        GemmArgs g = gemm_args(a.err, MAX_BLOCK, 1, U + (int64_t)i1 * ldu + i2, ldu, 1,
-                               W + i2, ldw, 1, N_out, K - i2, a.bw, -1.f, 1.f);
-        launch_gemm(g, st);
-      }
+    if (!done) {
+      GemmArgs g = gemm_args(a.err + e0, a.err_ld, 1, U + (int64_t)r0 * ldu + c0, ldu, 1,
+                             W + c0, ldw, 1, N_out, c1 - c0, k, -1.f, 1.f);
+      launch_gemm(g, st);
     }
+  };
+  for (int s0 = 0; s0 < K; s0 += super_cols) {
+    const int s1 = std::min(K, s0 + super_cols);
+    for (int i1 = s0; i1 < s1; i1 += blocksize) {
+      a.i1 = i1;
+      a.bw = std::min(blocksize, s1 - i1);
+      a.err_off = i1 - s0;
+      if (fast_layout && gpb != 0 && a.bw == MAX_BLOCK) {
+        const unsigned fgrid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, F_ROWS_PER_CTA),
+                                                           (int64_t)dgq_sm_count() * 3);
+        if (gpb == 1) gptq_block8_kernel<1><<<fgrid, F_WARPS * 32, smem, st>>>(a);
+        else if (gpb == 2) gptq_block8_kernel<2><<<fgrid, F_WARPS * 32, smem, st>>>(a);
+        else gptq_block8_kernel<4><<<fgrid, F_WARPS * 32, smem, st>>>(a);
+      } else {
+        gptq_block_kernel<<<grid, ROWS_PER_CTA * 32, (size_t)a.bw * MAX_BLOCK * sizeof(float), st>>>(a);
+      }
+      update(a.err_off, a.bw, i1, i1 + a.bw, s1);      // rest of this super-block
+    }
+    update(0, s1 - s0, s0, s1, K);                      // everything beyond it
   }
   return dgq_launch_status(dgq_cdiv(K, blocksize));
 }
