@@ -60,80 +60,141 @@ reverse_out_kernel(const float* __restrict__ V, int64_t ldv, float* __restrict__
 }
 
 // ---- leaf: Cholesky + inverse of one diagonal block ------------------------------------------
-// One CTA of 256 threads, the block lives in shared memory.  D (nb x nb, nb <= 64, lower
-// part read) is replaced by inv(chol(D)) (lower; the part above the diagonal is written as
-// zeros).  This kernel sits on the critical path K/64 times, so it is written for latency:
-//  * all 256 threads move the block in and out of shared memory;
-//  * factorisation, right-looking: row r = tid % 64 is shared by four threads that update
-//    every fourth entry of it; the pivot's reciprocal square root comes from rsqrt plus one
-//    Newton step (every thread computes it itself: no broadcast step), the column is
-//    broadcast through a double-buffered array so one barrier per step is enough for it;
-//  * inverse: thread t < 64 solves L x = e_t for column t by forward substitution, all
-//    threads walking the same row of L (a broadcast read) against their own column of X.
-// Loops are ordinary loops so that the code stays resident in the instruction cache.
+// One CTA of 256 threads.  D (nb x nb, nb <= 64, lower part read) is replaced by
+// inv(chol(D)) (lower; the part above the diagonal is written as zeros).  This kernel
+// sits on the critical path K/64 times, so it is written for latency.  The block is
+// treated as 2 x 2 tiles of 32 x 32:
+//   X11 = inv(chol(A11))                one warp, rows/columns in registers (below)
+//   L21 = A21 X11^T ; A22 -= L21 L21^T  all eight warps, operands in shared memory
+//   X22 = inv(chol(A22))                one warp
+//   X21 = -X22 (L21 X11)                all eight warps
+// chol32: lane i keeps row i of the tile in 32 registers, rotated so that the current
+// column always sits in register 0 (the shift is folded into the update's destination
+// register), pivots and column entries travel by warp shuffles - no barriers, no
+// dynamically indexed registers, and a rolled loop that stays in the instruction cache.
+// inv32: lane t keeps column t of the inverse the same way; the entries of L it needs are
+// the same for all lanes and are read from shared memory as broadcasts.
 constexpr int LEAF_THREADS = 256;
+constexpr int HT = 32;  // tile edge
 
-__global__ void __launch_bounds__(LEAF_THREADS)
-leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
-  __shared__ float S[NB][NB + 1];
-  __shared__ float X[NB][NB + 1];
-  __shared__ float colk[2][NB];
-  const int tid = threadIdx.x;
-  const int r = tid & (NB - 1);   // row owned during the factorisation
-  const int part = tid >> 6;      // which quarter of the row's entries
-#pragma unroll 4
-  for (int idx = tid; idx < NB * NB; idx += LEAF_THREADS) {
-    const int i = idx / NB, j = idx % NB;
-    S[i][j] = (i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f) : (i == j ? 1.f : 0.f);
-  }
-  __syncthreads();
-  for (int k = 0; k < NB; ++k) {
-    float d = S[k][k];
+// L (lower, including the diagonal) of the 32 x 32 tile at S[r0.., c0..] replaces it; the
+// entries above the diagonal are written as zeros.  One warp.
+__device__ __forceinline__ void chol32(float (*S)[NB + 1], float* rdiag, int r0, int lane,
+                                       int32_t* info, int pivot_base) {
+  float a[HT];
+#pragma unroll
+  for (int j = 0; j < HT; ++j) a[j] = S[r0 + lane][r0 + j];
+#pragma unroll 1
+  for (int k = 0; k < HT; ++k) {
+    float d = __shfl_sync(0xffffffffu, a[0], k);
     if (!(d > 0.f) || !isfinite(d)) {
-      if (tid == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
+      if (lane == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
         info[1] = pivot_base - k;
       d = 1.f;
     }
     float rs = rsqrtf(d);
     rs = rs * fmaf(-0.5f * d * rs, rs, 1.5f);   // one Newton step: 1/sqrt(d) to ~1 ulp
-    const float lik = (r == k) ? d * rs : (r > k ? S[r][k] * rs : 0.f);
-    float* ck = colk[k & 1];
-    if (part == 0) ck[r] = lik;
-    __syncthreads();
-    if (r > k) {
-      if (part == 0) S[r][k] = lik;
-      // entries j = k+1+part, k+5+part, ... <= r of row r, eight at a time with all loads
-      // of a batch issued before its stores
-      int j = k + 1 + part;
-      for (; j + 28 <= r; j += 32) {
-        float c[8], v[8];
+    const float l = (lane == k) ? d * rs : (lane > k ? a[0] * rs : 0.f);
+    S[r0 + lane][r0 + k] = l;
+    if (lane == k) rdiag[r0 + k] = rs;   // 1 / L[k][k], reused by the inverse
+    // all shuffles of the step are issued before the first dependent multiply-add, so
+    // that their latencies overlap instead of adding up
+    float lj[HT];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { c[u] = ck[j + 4 * u]; v[u] = S[r][j + 4 * u]; }
+    for (int j = 1; j < HT; ++j) lj[j] = __shfl_sync(0xffffffffu, l, (k + j) & (HT - 1));
+    // column k+j of the row moves from register j to register j-1 while it is updated
 #pragma unroll
-        for (int u = 0; u < 8; ++u) S[r][j + 4 * u] = fmaf(-lik, c[u], v[u]);
-      }
-      for (; j <= r; j += 4) S[r][j] = fmaf(-lik, ck[j], S[r][j]);
-    } else if (r == k && part == 0) {
-      S[r][k] = lik;
-    }
-    __syncthreads();  // the next pivot S[k+1][k+1] and the column buffer's reuse two steps on
+    for (int j = 1; j < HT; ++j) a[j - 1] = fmaf(-l, lj[j], a[j]);
+    a[HT - 1] = 0.f;
   }
-  // X = L^-1, column t; entries above the diagonal come out as exact zeros
-  if (tid < NB) {
-    const int t = tid;
-    for (int i = 0; i < NB; ++i) {
-      float a0 = (i == t) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      int k = 0;
-      for (; k + 3 < i; k += 4) {
-        a0 = fmaf(-S[i][k], X[k][t], a0);
-        a1 = fmaf(-S[i][k + 1], X[k + 1][t], a1);
-        a2 = fmaf(-S[i][k + 2], X[k + 2][t], a2);
-        a3 = fmaf(-S[i][k + 3], X[k + 3][t], a3);
-      }
-      for (; k < i; ++k) a0 = fmaf(-S[i][k], X[k][t], a0);
-      X[i][t] = (i >= t) ? __fdiv_rn((a0 + a1) + (a2 + a3), S[i][i]) : 0.f;
+}
+
+// X[r0.., r0..] = inverse of the lower-triangular tile L = S[r0.., r0..].  One warp.
+__device__ __forceinline__ void inv32(float (*S)[NB + 1], float (*X)[NB + 1], const float* rdiag,
+                                      int r0, int lane) {
+  float y[HT];
+#pragma unroll
+  for (int i = 0; i < HT; ++i) y[i] = (i == lane) ? 1.f : 0.f;
+#pragma unroll 1
+  for (int k = 0; k < HT; ++k) {
+    // column k of L first (independent of y), then the dependent arithmetic
+    float lk[HT];
+#pragma unroll
+    for (int i = 1; i < HT; ++i) lk[i] = S[r0 + min(k + i, HT - 1)][r0 + k];  // past the tile: dead
+    const float xk = y[0] * rdiag[r0 + k];                 // row k of X is final
+    X[r0 + k][r0 + lane] = xk;
+#pragma unroll
+    for (int i = 1; i < HT; ++i) y[i - 1] = fmaf(-lk[i], xk, y[i]);
+    y[HT - 1] = 0.f;
+  }
+}
+
+// C(32 x 32) = alpha * A * B (+ C0) on tiles in shared memory; element accessors are passed
+// as lambdas so that transposes cost nothing.  All 256 threads, 4 outputs each.
+template <typename FA, typename FB, typename FC>
+__device__ __forceinline__ void mm32(int tid, FA a_at, FB b_at, FC store) {
+  const int i = tid >> 3, j0 = (tid & 7) * 4;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+  for (int k = 0; k < HT; ++k) {
+    const float av = a_at(i, k);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = fmaf(av, b_at(k, j0 + e), acc[e]);
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) store(i, j0 + e, acc[e]);
+}
+
+__global__ void __launch_bounds__(LEAF_THREADS)
+leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
+  __shared__ float S[NB][NB + 1];
+  __shared__ float X[NB][NB + 1];
+  __shared__ float T1[HT][HT + 1];
+  __shared__ float T2[HT][HT + 1];
+  __shared__ float rdiag[NB];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  {
+    // all of a thread's global loads are issued before the first store to shared memory
+    float v[NB * NB / LEAF_THREADS];
+#pragma unroll
+    for (int e = 0; e < NB * NB / LEAF_THREADS; ++e) {
+      const int idx = tid + e * LEAF_THREADS, i = idx / NB, j = idx % NB;
+      v[e] = (i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f) : (i == j ? 1.f : 0.f);
+    }
+#pragma unroll
+    for (int e = 0; e < NB * NB / LEAF_THREADS; ++e) {
+      const int idx = tid + e * LEAF_THREADS, i = idx / NB, j = idx % NB;
+      S[i][j] = v[e];
+      X[i][j] = 0.f;
     }
   }
+  __syncthreads();
+  if (warp == 0) {
+    chol32(S, rdiag, 0, lane, info, pivot_base);
+    __syncwarp();
+    inv32(S, X, rdiag, 0, lane);
+  }
+  __syncthreads();
+  // L21 = A21 * X11^T
+  mm32(tid, [&](int i, int k) { return S[HT + i][k]; }, [&](int k, int j) { return X[j][k]; },
+       [&](int i, int j, float v) { T1[i][j] = v; });
+  __syncthreads();
+  // A22 -= L21 * L21^T
+  mm32(tid, [&](int i, int k) { return T1[i][k]; }, [&](int k, int j) { return T1[j][k]; },
+       [&](int i, int j, float v) { S[HT + i][HT + j] -= v; });
+  __syncthreads();
+  if (warp == 0) {
+    chol32(S, rdiag, HT, lane, info, pivot_base - HT);
+    __syncwarp();
+    inv32(S, X, rdiag, HT, lane);
+  }
+  __syncthreads();
+  // T2 = L21 * X11 ;  X21 = -X22 * T2
+  mm32(tid, [&](int i, int k) { return T1[i][k]; }, [&](int k, int j) { return X[k][j]; },
+       [&](int i, int j, float v) { T2[i][j] = v; });
+  __syncthreads();
+  mm32(tid, [&](int i, int k) { return X[HT + i][HT + k]; }, [&](int k, int j) { return T2[k][j]; },
+       [&](int i, int j, float v) { X[HT + i][j] = -v; });
   __syncthreads();
   for (int idx = tid; idx < NB * NB; idx += LEAF_THREADS) {
     const int i = idx / NB, j = idx % NB;
