@@ -182,6 +182,31 @@ class Sweep:
         for s in range(0, x.shape[0], CHUNK_SEQS):
             yield x[s:s + CHUNK_SEQS]
 
+    def _finish(self, item, from_host: bool, results: list):
+        """Layer-parallel quantization: the owner of a run quantizes and packs it."""
+        from distributed_gptq_b200 import _C
+        ri, q, work = item
+        if work is not None:
+            work.wait()
+        if self.owner[ri] != self.rank:
+            q.free_hessian()
+            return
+        bits = self.runs[ri][1]
+        stats = q.quantize()
+        fmt = _C.FMT_BYTES_LO_FIRST if bits == 4 else _C.FMT_INT32_LE
+        packed = q.pack_weights(format=fmt)
+        out = {"run": ri, "stats": stats, "qweight": packed["packed_weights"],
+               "scales": q.scale.to(torch.float16), "zeros": q.zero.to(torch.float16),
+               "g_idx": q.g_idx}
+        if from_host:
+            for k in ("qweight", "scales", "zeros", "g_idx"):
+                host = torch.empty(out[k].shape, dtype=out[k].dtype, pin_memory=True)
+                host.copy_(out[k], non_blocking=True)
+                self.d2h_bytes += host.numel() * host.element_size()
+                out[k] = host
+        results.append(out)
+        q.free_hessian()
+
     def step(self, from_host: bool):
         """One sweep.  Returns the packed results of the runs this rank owns."""
         import torch.distributed as dist
@@ -189,8 +214,25 @@ class Sweep:
         from distributed_gptq_b200 import GPTQ, _C
         dev = self.device
         self.h2d_bytes = self.d2h_bytes = 0
-        copy_stream = torch.cuda.Stream(device=dev) if from_host else None
-        quantizers, pending = [], []
+        staged = None
+        if from_host:
+            # Every layer's activations cross PCIe once per step: all host->device copies are
+            # queued on a side stream up front (inside the timed region) and each add_batch
+            # waits only for the chunk it consumes, so copies overlap the kernels.  The four
+            # runs of a layer read the same device copy.
+            copy_stream = torch.cuda.Stream(device=dev)
+            staged = []
+            with torch.cuda.stream(copy_stream):
+                for li in range(len(LAYERS)):
+                    chunks = []
+                    for c in self._chunks(self.X_host[li]):
+                        buf = c.to(dev, non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record(copy_stream)
+                        chunks.append((buf, ev))
+                        self.h2d_bytes += c.numel() * c.element_size()
+                    staged.append(chunks)
+        pending, results = [], []
         # ---- phase A: data-parallel Hessian accumulation, reduce to the owner
         for ri, (li, bits, act) in enumerate(self.runs):
             _, N_out, K = LAYERS[li]
@@ -199,50 +241,28 @@ class Sweep:
             q = GPTQ(lin, bits=bits, group_size=GROUP, actorder=act, percdamp=PERCDAMP,
                      blocksize=BLOCK, device=dev)
             if from_host:
-                # double-buffered host->device copies on a side stream, inside the timed region
-                chunks = list(self._chunks(self.X_host[li]))
-                nxt = None
-                for ci in range(len(chunks) + 1):
-                    cur = nxt
-                    if ci < len(chunks):
-                        with torch.cuda.stream(copy_stream):
-                            buf = chunks[ci].to(dev, non_blocking=True)
-                            ev = torch.cuda.Event()
-                            ev.record(copy_stream)
-                        self.h2d_bytes += chunks[ci].numel() * chunks[ci].element_size()
-                        nxt = (buf, ev)
-                    if cur is not None:
-                        torch.cuda.current_stream().wait_event(cur[1])
-                        q.add_batch(cur[0], None)
-                        cur[0].record_stream(torch.cuda.current_stream())
+                for buf, ev in staged[li]:
+                    torch.cuda.current_stream().wait_event(ev)
+                    q.add_batch(buf, None)
+                    buf.record_stream(torch.cuda.current_stream())
             else:
                 for c in self._chunks(self.X_dev[li]):
                     q.add_batch(c, None)
+            work = None
             if self.world > 1:
                 q.nsamples = NSEQ
-                pending.append(dist.reduce(q._Hbuf, dst=self.owner[ri], async_op=True))
-            quantizers.append(q)
-        for w in pending:
-            w.wait()
-        # ---- phase B: layer-parallel quantization of the runs this rank owns
-        results = []
-        for ri, (li, bits, act) in enumerate(self.runs):
-            q = quantizers[ri]
-            if self.owner[ri] != self.rank:
-                q.free_hessian()
-                continue
-            stats = q.quantize()
-            fmt = _C.FMT_BYTES_LO_FIRST if bits == 4 else _C.FMT_INT32_LE
-            packed = q.pack_weights(format=fmt)
-            out = {"run": ri, "stats": stats, "qweight": packed["packed_weights"],
-                   "scales": q.scale.to(torch.float16), "zeros": q.zero.to(torch.float16),
-                   "g_idx": q.g_idx}
-            if from_host:
-                for k in ("qweight", "scales", "zeros", "g_idx"):
-                    out[k] = out[k].cpu()
-                    self.d2h_bytes += out[k].numel() * out[k].element_size()
-            results.append(out)
-            q.free_hessian()
+                work = dist.reduce(q._Hbuf, dst=self.owner[ri], async_op=True)
+            pending.append((ri, q, work))
+            # One GPU: quantize right away, so that the kernels of the quantization overlap
+            # the host->device copies of the following layers.  Several GPUs: every reduce is
+            # a meeting point of all ranks, so all Hessians are accumulated and reduced first
+            # and the owners then quantize their runs side by side.
+            if self.world == 1:
+                self._finish(pending.pop(0), from_host, results)
+        while pending:
+            self._finish(pending.pop(0), from_host, results)
+        if from_host:
+            torch.cuda.current_stream().synchronize()   # the asynchronous result copies
         return results
 
 

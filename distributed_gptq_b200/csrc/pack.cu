@@ -294,6 +294,46 @@ unpack_dequant_kernel(const uint8_t* __restrict__ packed, const PT* __restrict__
   }
 }
 
+// Wide path for the layout the quantized layers store (4-bit, two codes per byte, low
+// nibble first) when rows are whole multiples of 32 columns and groups of 32: one thread
+// turns 16 packed bytes into 32 outputs with a single scale/zero pair, so the kernel
+// issues one 16-byte load and 64-128 bytes of 16-byte stores per thread.
+template <typename PT, typename OT>
+__global__ void __launch_bounds__(256)
+unpack_dequant_wide4_kernel(const uint4* __restrict__ packed, const PT* __restrict__ scales,
+                            const PT* __restrict__ zeros, OT* __restrict__ out, int rows, int cols,
+                            int n_groups, int group_size) {
+  const int vec_per_row = cols / 32;
+  const int64_t total = (int64_t)rows * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int c0 = (int)(i - r * vec_per_row) * 32;
+    const uint4 p = __ldg(packed + i);
+    const int g = n_groups == 1 ? 0 : c0 / group_size;
+    const float s = dgq_to_float<PT>(scales[r * n_groups + g]);
+    const float z = dgq_to_float<PT>(zeros[r * n_groups + g]);
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+    OT* dst = out + r * (int64_t)cols + c0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = dgq_dequant_level((float)((w[q] >> (4 * j)) & 0xF), s, z);
+      if (sizeof(OT) == 4) {
+        reinterpret_cast<float4*>(dst)[2 * q] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(dst)[2 * q + 1] = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+        alignas(16) OT t[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = dgq_from_float<OT>(v[j]);
+        reinterpret_cast<uint4*>(dst)[q] = *reinterpret_cast<const uint4*>(t);
+      }
+    }
+  }
+}
+
 bool valid_bits(int b) { return b == 2 || b == 3 || b == 4 || b == 8; }
 bool valid_fmt(int f) { return f >= 1 && f <= 3; }
 
@@ -389,6 +429,27 @@ int32_t launch_ud_out(const void* packed, const void* scales, const void* zeros,
   const uint8_t* p = reinterpret_cast<const uint8_t*>(packed);
   const PT* s = reinterpret_cast<const PT*>(scales);
   const PT* z = reinterpret_cast<const PT*>(zeros);
+  if (B == 4 && F == DGQ_FMT_BYTES_LO_FIRST && g_idx == nullptr && cols % 32 == 0 &&
+      (n_groups == 1 || group_size % 32 == 0) && dgq_aligned(packed, 16)) {
+    const unsigned wgrid = dgq_grid((int64_t)rows * (cols / 32), 256);
+    const uint4* p4 = reinterpret_cast<const uint4*>(packed);
+    switch (out_dtype) {
+      case DGQ_F32:
+        unpack_dequant_wide4_kernel<PT, float><<<wgrid, 256, 0, st>>>(
+            p4, s, z, reinterpret_cast<float*>(out), rows, cols, n_groups, group_size);
+        return dgq_launch_status();
+      case DGQ_F16:
+        unpack_dequant_wide4_kernel<PT, __half><<<wgrid, 256, 0, st>>>(
+            p4, s, z, reinterpret_cast<__half*>(out), rows, cols, n_groups, group_size);
+        return dgq_launch_status();
+      case DGQ_BF16:
+        unpack_dequant_wide4_kernel<PT, __nv_bfloat16><<<wgrid, 256, 0, st>>>(
+            p4, s, z, reinterpret_cast<__nv_bfloat16*>(out), rows, cols, n_groups, group_size);
+        return dgq_launch_status();
+      default:
+        return DGQ_ERR_ARG;
+    }
+  }
   switch (out_dtype) {
     case DGQ_F32:
       unpack_dequant_kernel<B, F, PT, float><<<grid, 256, 0, st>>>(

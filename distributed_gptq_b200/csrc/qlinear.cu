@@ -3,10 +3,9 @@
 // weight byte is read exactly once, activations are staged in shared memory per
 // 512-column slice and shared by all warps of the CTA.
 //
-// A warp owns ROWS_PER_WARP output features.  Per slice, a lane takes 8 consecutive
-// input columns at a time: 4 bytes of nibble pairs (4-bit) or 8 code bytes
-// (other widths), dequantizes them with the column's group scale/zero (through
-// g_idx when given) and accumulates against up to 16 batch rows in fp32.
+// qlinear_kernel (K a multiple of 8) is the main kernel; qlinear_generic_kernel covers
+// ragged K.  Both accumulate up to 16 batch rows in fp32 and dequantize with the column's
+// group scale/zero (through g_idx when given).
 #include "common.cuh"
 
 namespace {
@@ -33,7 +32,7 @@ __device__ __forceinline__ float load_bias(const void* b, int dt, int n) {
 
 template <typename XT, int MC, bool FOURBIT>
 __global__ void __launch_bounds__(WARPS * 32)
-qlinear_kernel(const LinArgs a, int m0) {
+qlinear_generic_kernel(const LinArgs a, int m0) {
   __shared__ __align__(16) float xs[MC][SLICE];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = blockIdx.x * ROWS_PER_CTA + warp * ROWS_PER_WARP;
@@ -130,13 +129,148 @@ qlinear_kernel(const LinArgs a, int m0) {
   }
 }
 
+// ---- main kernel: K a multiple of 8 -----------------------------------------------------------
+// A CTA owns 8 warps x R consecutive output features and walks K in slices.  Per slice the
+// activations are staged in shared memory as fp32, split per 8-column chunk into a low and
+// a high float4 stored in separate planes, so that lane l reading chunk (32 i + l) touches
+// consecutive 16-byte words (no bank conflicts).  A lane takes the chunks l, l+32, ... of a
+// row: one 4-byte load of nibble pairs (or 8 code bytes), the integer -> float conversion by
+// the 2^23 trick, one fused multiply-add per code for (code - zero) * scale, and M
+// multiply-adds per code against the staged activations.
+template <int MC>
+struct FastCfg {
+  static constexpr int R = (MC >= 8) ? 4 : 8;                       // rows per warp
+  static constexpr int SLICE = (MC >= 16) ? 768 : (MC >= 8 ? 1536 : (MC >= 4 ? 3072 : 4096));
+};
+
+__device__ __forceinline__ float nibble_to_float(uint32_t w, int j) {
+  return __uint_as_float(0x4B000000u | ((w >> (4 * j)) & 0xFu)) - 8388608.f;
+}
+__device__ __forceinline__ float byte_to_float(uint32_t w, int j) {
+  return __uint_as_float(0x4B000000u | ((w >> (8 * j)) & 0xFFu)) - 8388608.f;
+}
+
+template <typename XT, int MC, bool FOURBIT>
+__global__ void __launch_bounds__(WARPS * 32)
+qlinear_kernel(const LinArgs a, int m0) {
+  constexpr int R = FastCfg<MC>::R;
+  constexpr int SLICE = FastCfg<MC>::SLICE;
+  constexpr int SCH = SLICE / 8;                       // chunks per slice
+  extern __shared__ float4 xs4[];                      // [MC][2][SCH]
+  float* xs = reinterpret_cast<float*>(xs4);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = (blockIdx.x * WARPS + warp) * R;
+  const XT* x = reinterpret_cast<const XT*>(a.x) + (int64_t)m0 * a.K;
+  const int mrows = min(MC, a.M - m0);
+  const bool grouped_fast = (a.g_idx == nullptr) && (a.n_groups == 1 || a.group_size % 8 == 0);
+
+  float acc[R][MC];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < MC; ++m) acc[r][m] = 0.f;
+
+  for (int k0 = 0; k0 < a.K; k0 += SLICE) {
+    const int kcols = min(SLICE, a.K - k0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < MC * SLICE; idx += blockDim.x) {
+      const int m = idx / SLICE, c = idx - m * SLICE;
+      const float v = (m < mrows && c < kcols) ? dgq_to_float<XT>(x[(int64_t)m * a.K + k0 + c]) : 0.f;
+      xs[((m * 2 + ((c >> 2) & 1)) * SCH + (c >> 3)) * 4 + (c & 3)] = v;
+    }
+    __syncthreads();
+    const int nch = kcols >> 3;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int n = n0 + r;
+      if (n >= a.N_out) break;
+      const uint8_t* wrow = a.qw + (int64_t)n * a.row_bytes + (FOURBIT ? (k0 >> 1) : k0);
+      const __half* srow = a.scales + (int64_t)n * a.n_groups;
+      const __half* zrow = a.zeros + (int64_t)n * a.n_groups;
+#pragma unroll 2
+      for (int ch = lane; ch < nch; ch += 32) {
+        uint32_t w0, w1 = 0;
+        if (FOURBIT) {
+          w0 = __ldg(reinterpret_cast<const uint32_t*>(wrow) + ch);
+        } else {
+          const uint2 t = __ldg(reinterpret_cast<const uint2*>(wrow) + ch);
+          w0 = t.x; w1 = t.y;
+        }
+        const int c = k0 + ch * 8;
+        float wf[8];
+        if (grouped_fast) {
+          const int g = a.n_groups == 1 ? 0 : c / a.group_size;
+          const float s = __half2float(srow[g]);
+          const float nzs = -__half2float(zrow[g]) * s;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float q = FOURBIT ? nibble_to_float(w0, j)
+                                    : byte_to_float(j < 4 ? w0 : w1, j & 3);
+            wf[j] = fmaf(q, s, nzs);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int g = a.g_idx ? a.g_idx[c + j] : (c + j) / a.group_size;
+            const float s = __half2float(srow[g]);
+            const float q = FOURBIT ? nibble_to_float(w0, j)
+                                    : byte_to_float(j < 4 ? w0 : w1, j & 3);
+            wf[j] = fmaf(q, s, -__half2float(zrow[g]) * s);
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < MC; ++m) {
+          const float4 lo = xs4[(m * 2 + 0) * SCH + ch];
+          const float4 hi = xs4[(m * 2 + 1) * SCH + ch];
+          float t = acc[r][m];
+          t = fmaf(wf[0], lo.x, t); t = fmaf(wf[1], lo.y, t);
+          t = fmaf(wf[2], lo.z, t); t = fmaf(wf[3], lo.w, t);
+          t = fmaf(wf[4], hi.x, t); t = fmaf(wf[5], hi.y, t);
+          t = fmaf(wf[6], hi.z, t); t = fmaf(wf[7], hi.w, t);
+          acc[r][m] = t;
+        }
+      }
+    }
+  }
+  XT* y = reinterpret_cast<XT*>(a.y);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int n = n0 + r;
+#pragma unroll
+    for (int m = 0; m < MC; ++m) {
+      float v = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && n < a.N_out && m < mrows) {
+        if (a.bias) v += load_bias<XT>(a.bias, a.bias_dtype, n);
+        y[(int64_t)(m0 + m) * a.N_out + n] = dgq_from_float<XT>(v);
+      }
+    }
+  }
+}
+
+template <typename XT, int MC>
+void launch_fast(const LinArgs& a, int m0, cudaStream_t st) {
+  constexpr int R = FastCfg<MC>::R;
+  const unsigned grid = (unsigned)dgq_cdiv(a.N_out, WARPS * R);
+  const size_t smem = (size_t)MC * FastCfg<MC>::SLICE * sizeof(float);
+  if (a.bits == 4)
+    qlinear_kernel<XT, MC, true><<<grid, WARPS * 32, smem, st>>>(a, m0);
+  else
+    qlinear_kernel<XT, MC, false><<<grid, WARPS * 32, smem, st>>>(a, m0);
+}
+
 template <typename XT, int MC>
 void launch_mc(const LinArgs& a, int m0, cudaStream_t st) {
+  if (a.K % 8 == 0) {
+    launch_fast<XT, MC>(a, m0, st);
+    return;
+  }
   unsigned grid = (unsigned)dgq_cdiv(a.N_out, ROWS_PER_CTA);
   if (a.bits == 4)
-    qlinear_kernel<XT, MC, true><<<grid, WARPS * 32, 0, st>>>(a, m0);
+    qlinear_generic_kernel<XT, MC, true><<<grid, WARPS * 32, 0, st>>>(a, m0);
   else
-    qlinear_kernel<XT, MC, false><<<grid, WARPS * 32, 0, st>>>(a, m0);
+    qlinear_generic_kernel<XT, MC, false><<<grid, WARPS * 32, 0, st>>>(a, m0);
 }
 
 template <typename XT>

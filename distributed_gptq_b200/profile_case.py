@@ -32,6 +32,21 @@ def _time(fn, reps):
     return out
 
 
+def _time_raw(call, reps, inner=50):
+    """Average time of `inner` back-to-back raw library calls (no Python wrapper work in
+    between, so kernels of a few microseconds are not hidden behind host overhead)."""
+    out = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(inner):
+            call()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) / inner)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["hessian", "inv_chol", "quantize", "pack", "dequant", "qlinear"])
@@ -83,8 +98,13 @@ def main():
                       f"{N * K * (K - 128) / t / 1e9:.2f} TFLOP/s")
     elif a.case in ("pack", "dequant"):
         codes = torch.randint(0, 2 ** a.bits, (N, K), generator=g, device=dev, dtype=torch.uint8)
+        import ctypes
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        L = _C.lib()
         if a.case == "pack":
-            for t in _time(lambda: _C.pack(codes, a.bits, _C.FMT_BYTES_LO_FIRST), a.reps):
+            outp = _C.pack(codes, a.bits, _C.FMT_BYTES_LO_FIRST)
+            call = lambda: L.dgq_pack(P(codes), N, K, a.bits, _C.FMT_BYTES_LO_FIRST, P(outp), None)
+            for t in _time_raw(call, a.reps):
                 nbytes = N * K * (1 + a.bits / 8)
                 print(f"pack N={N} K={K} bits={a.bits}: {t:.3f} ms  {nbytes / t / 1e6:.1f} GB/s")
         else:
@@ -92,9 +112,10 @@ def main():
             ng = K // 128
             s = torch.rand(N, ng, generator=g, device=dev).half()
             z = torch.randint(0, 2 ** a.bits, (N, ng), generator=g, device=dev).half()
-            fn = lambda: _C.unpack_dequant(packed, s, z, None, K, a.bits, 128,
-                                           _C.FMT_BYTES_LO_FIRST, torch.bfloat16)
-            for t in _time(fn, a.reps):
+            outd = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
+            call = lambda: L.dgq_unpack_dequant(P(packed), P(s), P(z), None, N, K, ng, a.bits, 128,
+                                                _C.FMT_BYTES_LO_FIRST, _C.F16, _C.BF16, P(outd), None)
+            for t in _time_raw(call, a.reps):
                 nbytes = N * K * (a.bits / 8 + 2) + 4 * N * ng
                 print(f"unpack_dequant N={N} K={K} bits={a.bits}: {t:.3f} ms  {nbytes / t / 1e6:.1f} GB/s")
     else:
@@ -104,8 +125,13 @@ def main():
         s = torch.rand(N, ng, generator=g, device=dev).half() * 0.01
         z = torch.randint(0, 16, (N, ng), generator=g, device=dev).half()
         x = torch.randn(a.M, K, generator=g, device=dev).to(torch.bfloat16)
-        fn = lambda: _C.qlinear_forward(x, qw, s, z, None, None, K, 4, 128)
-        for t in _time(fn, a.reps):
+        import ctypes
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        y = torch.empty((a.M, N), dtype=torch.bfloat16, device=dev)
+        L = _C.lib()
+        call = lambda: L.dgq_qlinear_forward(P(x), _C.BF16, a.M, P(qw), P(s), P(z), None, None, 0, N, K,
+                                             ng, 4, 128, P(y), None)
+        for t in _time_raw(call, a.reps):
             nbytes = N * K / 2 + 4 * N * ng + 2 * a.M * (K + N)
             print(f"qlinear M={a.M} N={N} K={K}: {t * 1e3:.1f} us  {nbytes / t / 1e6:.1f} GB/s")
 
