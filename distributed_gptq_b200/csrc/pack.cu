@@ -295,40 +295,47 @@ unpack_dequant_kernel(const uint8_t* __restrict__ packed, const PT* __restrict__
 }
 
 // Wide path for the layout the quantized layers store (4-bit, two codes per byte, low
-// nibble first) when rows are whole multiples of 32 columns and groups of 32: one thread
-// turns 16 packed bytes into 32 outputs with a single scale/zero pair, so the kernel
-// issues one 16-byte load and 64-128 bytes of 16-byte stores per thread.
+// nibble first) when rows hold whole 8-column words and groups are multiples of 8 columns.
+// The matrix is walked as a flat array of 32-bit words (8 codes each).  A thread handles
+// four words that are 32 words apart, so that every load instruction of a warp reads 128
+// consecutive bytes and every store instruction writes 512 (bf16/fp16) or 1024 (fp32)
+// consecutive bytes; the four independent loads are in flight together.
 template <typename PT, typename OT>
 __global__ void __launch_bounds__(256)
-unpack_dequant_wide4_kernel(const uint4* __restrict__ packed, const PT* __restrict__ scales,
-                            const PT* __restrict__ zeros, OT* __restrict__ out, int rows, int cols,
-                            int n_groups, int group_size) {
-  const int vec_per_row = cols / 32;
-  const int64_t total = (int64_t)rows * vec_per_row;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / vec_per_row;
-    const int c0 = (int)(i - r * vec_per_row) * 32;
-    const uint4 p = __ldg(packed + i);
-    const int g = n_groups == 1 ? 0 : c0 / group_size;
-    const float s = dgq_to_float<PT>(scales[r * n_groups + g]);
-    const float z = dgq_to_float<PT>(zeros[r * n_groups + g]);
-    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
-    OT* dst = out + r * (int64_t)cols + c0;
+unpack_dequant_wide4_kernel(const uint32_t* __restrict__ packed, const PT* __restrict__ scales,
+                            const PT* __restrict__ zeros, OT* __restrict__ out, int64_t n_words,
+                            int words_per_row, int n_groups, int group_size) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t base = warp_global * 128; base < n_words; base += n_warps * 128) {
+    uint32_t w[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
+      const int64_t wi = base + q * 32 + lane;
+      w[q] = wi < n_words ? __ldg(packed + wi) : 0u;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int64_t wi = base + q * 32 + lane;
+      if (wi >= n_words) continue;
+      const int64_t r = wi / words_per_row;
+      const int c0 = (int)(wi - r * words_per_row) * 8;
+      const int g = n_groups == 1 ? 0 : c0 / group_size;
+      const float s = dgq_to_float<PT>(scales[r * n_groups + g]);
+      const float z = dgq_to_float<PT>(zeros[r * n_groups + g]);
       float v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        v[j] = dgq_dequant_level((float)((w[q] >> (4 * j)) & 0xF), s, z);
+      for (int j = 0; j < 8; ++j) v[j] = dgq_dequant_level((float)((w[q] >> (4 * j)) & 0xF), s, z);
+      OT* dst = out + wi * 8;
       if (sizeof(OT) == 4) {
-        reinterpret_cast<float4*>(dst)[2 * q] = make_float4(v[0], v[1], v[2], v[3]);
-        reinterpret_cast<float4*>(dst)[2 * q + 1] = make_float4(v[4], v[5], v[6], v[7]);
+        reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
       } else {
         alignas(16) OT t[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) t[j] = dgq_from_float<OT>(v[j]);
-        reinterpret_cast<uint4*>(dst)[q] = *reinterpret_cast<const uint4*>(t);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(t);
       }
     }
   }
@@ -429,22 +436,24 @@ int32_t launch_ud_out(const void* packed, const void* scales, const void* zeros,
   const uint8_t* p = reinterpret_cast<const uint8_t*>(packed);
   const PT* s = reinterpret_cast<const PT*>(scales);
   const PT* z = reinterpret_cast<const PT*>(zeros);
-  if (B == 4 && F == DGQ_FMT_BYTES_LO_FIRST && g_idx == nullptr && cols % 32 == 0 &&
-      (n_groups == 1 || group_size % 32 == 0) && dgq_aligned(packed, 16)) {
-    const unsigned wgrid = dgq_grid((int64_t)rows * (cols / 32), 256);
-    const uint4* p4 = reinterpret_cast<const uint4*>(packed);
+  if (B == 4 && F == DGQ_FMT_BYTES_LO_FIRST && g_idx == nullptr && cols % 8 == 0 &&
+      (n_groups == 1 || group_size % 8 == 0) && dgq_aligned(packed, 4)) {
+    const int64_t n_words = (int64_t)rows * (cols / 8);
+    const unsigned wgrid = dgq_grid(dgq_cdiv(n_words, 4), 256);
+    const uint32_t* p4 = reinterpret_cast<const uint32_t*>(packed);
     switch (out_dtype) {
       case DGQ_F32:
         unpack_dequant_wide4_kernel<PT, float><<<wgrid, 256, 0, st>>>(
-            p4, s, z, reinterpret_cast<float*>(out), rows, cols, n_groups, group_size);
+            p4, s, z, reinterpret_cast<float*>(out), n_words, cols / 8, n_groups, group_size);
         return dgq_launch_status();
       case DGQ_F16:
         unpack_dequant_wide4_kernel<PT, __half><<<wgrid, 256, 0, st>>>(
-            p4, s, z, reinterpret_cast<__half*>(out), rows, cols, n_groups, group_size);
+            p4, s, z, reinterpret_cast<__half*>(out), n_words, cols / 8, n_groups, group_size);
         return dgq_launch_status();
       case DGQ_BF16:
         unpack_dequant_wide4_kernel<PT, __nv_bfloat16><<<wgrid, 256, 0, st>>>(
-            p4, s, z, reinterpret_cast<__nv_bfloat16*>(out), rows, cols, n_groups, group_size);
+            p4, s, z, reinterpret_cast<__nv_bfloat16*>(out), n_words, cols / 8, n_groups,
+            group_size);
         return dgq_launch_status();
       default:
         return DGQ_ERR_ARG;

@@ -21,6 +21,7 @@ struct LinArgs {
   const __half* scales; const __half* zeros; const int32_t* g_idx;
   const void* bias; int bias_dtype;
   int M, N_out, K, n_groups, group_size, bits;
+  int vec16;   // rows of qweight start on 16-byte boundaries
 };
 
 template <typename XT>
@@ -132,11 +133,12 @@ qlinear_generic_kernel(const LinArgs a, int m0) {
 // ---- main kernel: K a multiple of 8 -----------------------------------------------------------
 // A CTA owns 8 warps x R consecutive output features and walks K in slices.  Per slice the
 // activations are staged in shared memory as fp32, split per 8-column chunk into a low and
-// a high float4 stored in separate planes, so that lane l reading chunk (32 i + l) touches
-// consecutive 16-byte words (no bank conflicts).  A lane takes the chunks l, l+32, ... of a
-// row: one 4-byte load of nibble pairs (or 8 code bytes), the integer -> float conversion by
-// the 2^23 trick, one fused multiply-add per code for (code - zero) * scale, and M
-// multiply-adds per code against the staged activations.
+// a high float4, stored so that lane l reading 32-column quad (32 i + l) touches consecutive
+// 16-byte words (no bank conflicts).  A lane takes the quads l, l+32, ... of R rows at once:
+// one 16-byte load of nibble pairs per row (all R in flight together), the integer -> float
+// conversion by the 2^23 trick, one fused multiply-add per code for (code - zero) * scale,
+// and M multiply-adds per code against the staged activations, which are read once per
+// quad for all R rows.
 template <int MC>
 struct FastCfg {
   static constexpr int R = (MC >= 8) ? 4 : 8;                       // rows per warp
@@ -155,8 +157,9 @@ __global__ void __launch_bounds__(WARPS * 32)
 qlinear_kernel(const LinArgs a, int m0) {
   constexpr int R = FastCfg<MC>::R;
   constexpr int SLICE = FastCfg<MC>::SLICE;
-  constexpr int SCH = SLICE / 8;                       // chunks per slice
-  extern __shared__ float4 xs4[];                      // [MC][2][SCH]
+  constexpr int SCH = SLICE / 8;                       // 8-column chunks per slice
+  constexpr int SQ = SCH / 4;                          // 32-column quads per slice
+  extern __shared__ float4 xs4[];                      // [MC][2 halves][4 sub-chunks][SQ]
   float* xs = reinterpret_cast<float*>(xs4);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = (blockIdx.x * WARPS + warp) * R;
@@ -173,61 +176,94 @@ qlinear_kernel(const LinArgs a, int m0) {
   for (int k0 = 0; k0 < a.K; k0 += SLICE) {
     const int kcols = min(SLICE, a.K - k0);
     __syncthreads();
+    // column c of the slice = quad (c >> 5), sub-chunk ((c >> 3) & 3), half ((c >> 2) & 1),
+    // element (c & 3); quads are the fastest index so that lane l reading quad (32 i + l)
+    // touches consecutive 16-byte words
     for (int idx = threadIdx.x; idx < MC * SLICE; idx += blockDim.x) {
       const int m = idx / SLICE, c = idx - m * SLICE;
       const float v = (m < mrows && c < kcols) ? dgq_to_float<XT>(x[(int64_t)m * a.K + k0 + c]) : 0.f;
-      xs[((m * 2 + ((c >> 2) & 1)) * SCH + (c >> 3)) * 4 + (c & 3)] = v;
+      xs[((((m * 2 + ((c >> 2) & 1)) * 4 + ((c >> 3) & 3)) * SQ) + (c >> 5)) * 4 + (c & 3)] = v;
     }
     __syncthreads();
-    const int nch = kcols >> 3;
+    const int nquads = (kcols + 31) >> 5;   // a ragged last quad reads zero-padded activations
+    for (int qd = lane; qd < nquads; qd += 32) {
+      // the R rows' loads of this quad are independent and in flight together:
+      // 16 bytes of nibble pairs (32 codes) or 2 x 16 bytes of code bytes per row
+      uint32_t w[R][FOURBIT ? 4 : 8];
+      const bool whole = a.vec16 && (qd * 32 + 32 <= kcols);
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int n = n0 + r;
-      if (n >= a.N_out) break;
-      const uint8_t* wrow = a.qw + (int64_t)n * a.row_bytes + (FOURBIT ? (k0 >> 1) : k0);
-      const __half* srow = a.scales + (int64_t)n * a.n_groups;
-      const __half* zrow = a.zeros + (int64_t)n * a.n_groups;
-#pragma unroll 2
-      for (int ch = lane; ch < nch; ch += 32) {
-        uint32_t w0, w1 = 0;
+      for (int r = 0; r < R; ++r) {
+        const int n = min(n0 + r, a.N_out - 1);   // rows past the end shadow the last row
+        const uint8_t* wrow = a.qw + (int64_t)n * a.row_bytes + (FOURBIT ? (k0 >> 1) : k0);
         if (FOURBIT) {
-          w0 = __ldg(reinterpret_cast<const uint32_t*>(wrow) + ch);
-        } else {
-          const uint2 t = __ldg(reinterpret_cast<const uint2*>(wrow) + ch);
-          w0 = t.x; w1 = t.y;
-        }
-        const int c = k0 + ch * 8;
-        float wf[8];
-        if (grouped_fast) {
-          const int g = a.n_groups == 1 ? 0 : c / a.group_size;
-          const float s = __half2float(srow[g]);
-          const float nzs = -__half2float(zrow[g]) * s;
+          if (whole) {
+            const uint4 t = __ldg(reinterpret_cast<const uint4*>(wrow) + qd);
+            w[r][0] = t.x; w[r][1] = t.y; w[r][2] = t.z; w[r][3] = t.w;
+          } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float q = FOURBIT ? nibble_to_float(w0, j)
-                                    : byte_to_float(j < 4 ? w0 : w1, j & 3);
-            wf[j] = fmaf(q, s, nzs);
+            for (int q = 0; q < 4; ++q)
+              w[r][q] = (qd * 32 + q * 8 < kcols)
+                            ? __ldg(reinterpret_cast<const uint32_t*>(wrow) + qd * 4 + q) : 0u;
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int g = a.g_idx ? a.g_idx[c + j] : (c + j) / a.group_size;
-            const float s = __half2float(srow[g]);
-            const float q = FOURBIT ? nibble_to_float(w0, j)
-                                    : byte_to_float(j < 4 ? w0 : w1, j & 3);
-            wf[j] = fmaf(q, s, -__half2float(zrow[g]) * s);
+          for (int q = 0; q < 4; ++q) {
+            uint2 t = make_uint2(0u, 0u);
+            if (qd * 32 + q * 8 < kcols) t = __ldg(reinterpret_cast<const uint2*>(wrow) + qd * 4 + q);
+            w[r][2 * q] = t.x; w[r][2 * q + 1] = t.y;
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int c = k0 + qd * 32 + q * 8;
+        if (c >= a.K) break;
+        float wf[R][8];
+        if (grouped_fast) {
+          const int g = a.n_groups == 1 ? 0 : c / a.group_size;
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const int n = min(n0 + r, a.N_out - 1);
+            const float s = __half2float(a.scales[(int64_t)n * a.n_groups + g]);
+            const float nzs = -__half2float(a.zeros[(int64_t)n * a.n_groups + g]) * s;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float cq = FOURBIT ? nibble_to_float(w[r][q], j)
+                                       : byte_to_float(w[r][(FOURBIT ? 0 : 2 * q) + (j >> 2)], j & 3);
+              wf[r][j] = fmaf(cq, s, nzs);
+            }
+          }
+        } else {
+          int gj[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) gj[j] = a.g_idx ? a.g_idx[c + j] : (c + j) / a.group_size;
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const int n = min(n0 + r, a.N_out - 1);
+            const __half* srow = a.scales + (int64_t)n * a.n_groups;
+            const __half* zrow = a.zeros + (int64_t)n * a.n_groups;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float s = __half2float(srow[gj[j]]);
+              const float cq = FOURBIT ? nibble_to_float(w[r][q], j)
+                                       : byte_to_float(w[r][(FOURBIT ? 0 : 2 * q) + (j >> 2)], j & 3);
+              wf[r][j] = fmaf(cq, s, -__half2float(zrow[gj[j]]) * s);
+            }
           }
         }
 #pragma unroll
         for (int m = 0; m < MC; ++m) {
-          const float4 lo = xs4[(m * 2 + 0) * SCH + ch];
-          const float4 hi = xs4[(m * 2 + 1) * SCH + ch];
-          float t = acc[r][m];
-          t = fmaf(wf[0], lo.x, t); t = fmaf(wf[1], lo.y, t);
-          t = fmaf(wf[2], lo.z, t); t = fmaf(wf[3], lo.w, t);
-          t = fmaf(wf[4], hi.x, t); t = fmaf(wf[5], hi.y, t);
-          t = fmaf(wf[6], hi.z, t); t = fmaf(wf[7], hi.w, t);
-          acc[r][m] = t;
+          const float4 lo = xs4[((m * 2 + 0) * 4 + q) * SQ + qd];
+          const float4 hi = xs4[((m * 2 + 1) * 4 + q) * SQ + qd];
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            float t = acc[r][m];
+            t = fmaf(wf[r][0], lo.x, t); t = fmaf(wf[r][1], lo.y, t);
+            t = fmaf(wf[r][2], lo.z, t); t = fmaf(wf[r][3], lo.w, t);
+            t = fmaf(wf[r][4], hi.x, t); t = fmaf(wf[r][5], hi.y, t);
+            t = fmaf(wf[r][6], hi.z, t); t = fmaf(wf[r][7], hi.w, t);
+            acc[r][m] = t;
+          }
         }
       }
     }
@@ -307,6 +343,7 @@ DGQ_EXPORT int32_t dgq_qlinear_forward(const void* x, int32_t x_dtype, int32_t M
   a.zeros = reinterpret_cast<const __half*>(zeros_f16);
   a.g_idx = g_idx; a.bias = bias; a.bias_dtype = bias_dtype;
   a.M = M; a.N_out = N_out; a.K = K; a.n_groups = n_groups; a.group_size = group_size; a.bits = bits;
+  a.vec16 = (a.row_bytes % 16 == 0 && dgq_aligned(qweight, 16)) ? 1 : 0;
   DGQ_REQUIRE(K % 8 != 0 || dgq_aligned(qweight, 8), DGQ_ERR_ALIGN);
   cudaStream_t st = dgq_stream(stream);
   if (x_dtype == DGQ_F32) launch_all<float>(a, st);
