@@ -7,8 +7,9 @@
 // lo = x - hi, writing hi in place and lo into a twin buffer at the same (swizzled)
 // offset; one thread then issues, per 8 reduction steps, three tcgen05.mma kind::tf32
 // instructions (hi*hi, hi*lo, lo*hi) into a 128 x 128 fp32 accumulator in tensor memory.
-// Accumulators are double buffered so that the epilogue warps (TMEM -> registers ->
-// alpha/beta update -> global) overlap the next tile's main loop.  CTAs are persistent
+// Accumulators are double buffered so that the epilogue warps (TMEM -> registers -> a
+// warp-private swizzled staging tile in shared memory -> alpha/beta update with whole
+// 128-byte lines of C per row) overlap the next tile's main loop.  CTAs are persistent
 // over the output tiles.
 //
 // Warps: 0 TMA producer (+ TMEM allocation), 1 MMA issuer, 2-5 converters, 6-9 epilogue.
@@ -29,7 +30,8 @@ constexpr int STAGE_BYTES = 4 * OPERAND_BYTES;     // A hi, A lo, B hi, B lo
 constexpr int STAGES = 3;
 constexpr int THREADS = 320;
 constexpr uint32_t TMEM_COLS = 256;                // two 128-column accumulators
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_STAGE_BYTES = 4 * 32 * 128;        // per epilogue warp: 32 rows x 32 fp32 columns
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256;
 
 struct Control {
   uint64_t full[STAGES], conv[STAGES], empty[STAGES];
@@ -85,7 +87,8 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* stages = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  Control* ctl = reinterpret_cast<Control*>(stages + (size_t)STAGES * STAGE_BYTES);
+  uint8_t* epi_stage = stages + (size_t)STAGES * STAGE_BYTES;
+  Control* ctl = reinterpret_cast<Control*>(epi_stage + EPI_STAGE_BYTES);
   volatile int* abort_flag = &ctl->abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -247,43 +250,69 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         break;
       }
       tc05::fence_after_sync();
-      const int row = w.ti * TILE + q * 32 + lane;
-      float* crow = p.c + (int64_t)row * p.ldc;
+      // Each warp drains its 32 accumulator rows 32 columns at a time: TMEM -> registers
+      // (one row per lane) -> this warp's 4 KB of shared memory (16-byte pieces XOR-swizzled
+      // by the row so that neither side has bank conflicts) -> global memory with eight
+      // lanes per row, i.e. every load/store instruction touches four whole 128-byte lines.
+      float4* mine = reinterpret_cast<float4*>(epi_stage) + (warp - 6) * (32 * 8);
+      const int row0 = w.ti * TILE + q * 32;
 #pragma unroll 1
       for (int chunk = 0; chunk < TILE / 32; ++chunk) {
+        const int c0 = w.tj * TILE + chunk * 32;
+        const bool live = (row0 < p.m && c0 < p.n);   // uniform across the warp
+        // this lane's eight 16-byte pieces of C: rows row0 + 4 it + lane/8, columns c0 + 4 (lane%8)
+        const int c = c0 + 4 * (lane & 7);
+        float4 old[8];
+        bool ok[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int row = row0 + it * 4 + (lane >> 3);
+          // whole float4 inside the matrix (and, for a lower-triangular result, not right of
+          // the diagonal); ragged pieces take the scalar path below
+          ok[it] = live && row < p.m && c + 3 < p.n && (!p.lower_only || c + 3 <= row);
+          old[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (p.beta != 0.f) {
+          // all loads of the chunk are issued before anything waits on them
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int row = row0 + it * 4 + (lane >> 3);
+            if (ok[it]) old[it] = *reinterpret_cast<const float4*>(p.c + (int64_t)row * p.ldc + c);
+          }
+        }
         uint32_t v[32];
         tc05::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE + chunk * 32, v);
         tc05::tmem_ld_wait();
-        const int c0 = w.tj * TILE + chunk * 32;
-        if (row >= p.m || c0 >= p.n) continue;
+        if (!live) continue;
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const int c = c0 + j;
-          if (c >= p.n) break;
-          if (p.lower_only && c > row) break;
-          float o[4];
+        for (int c4 = 0; c4 < 8; ++c4)
+          mine[lane * 8 + (c4 ^ (lane & 7))] =
+              make_float4(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]),
+                          __uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3]));
+        __syncwarp();
 #pragma unroll
-          for (int e = 0; e < 4; ++e) o[e] = p.alpha * __uint_as_float(v[j + e]);
-          const bool full4 = (c + 3 < p.n) && (!p.lower_only || c + 3 <= row);
-          if (full4) {
-            float4* dst = reinterpret_cast<float4*>(crow + c);
-            if (p.beta != 0.f) {
-              const float4 old = *dst;
-              o[0] += p.beta * old.x; o[1] += p.beta * old.y;
-              o[2] += p.beta * old.z; o[3] += p.beta * old.w;
-            }
-            *dst = make_float4(o[0], o[1], o[2], o[3]);
-          } else {
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + (lane >> 3), c4 = lane & 7;
+          const int row = row0 + rr;
+          const float4 acc = mine[rr * 8 + (c4 ^ (rr & 7))];
+          float* cp = p.c + (int64_t)row * p.ldc + c;
+          if (ok[it]) {
+            *reinterpret_cast<float4*>(cp) =
+                make_float4(fmaf(p.alpha, acc.x, p.beta * old[it].x), fmaf(p.alpha, acc.y, p.beta * old[it].y),
+                            fmaf(p.alpha, acc.z, p.beta * old[it].z), fmaf(p.alpha, acc.w, p.beta * old[it].w));
+          } else if (row < p.m && c < p.n) {
+            const float o[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               if (c + e < p.n && (!p.lower_only || c + e <= row)) {
-                float val = o[e];
-                if (p.beta != 0.f) val += p.beta * crow[c + e];
-                crow[c + e] = val;
+                float val = p.alpha * o[e];
+                if (p.beta != 0.f) val += p.beta * cp[e];
+                cp[e] = val;
               }
             }
           }
         }
+        __syncwarp();   // the staging rows are rewritten by the next chunk
       }
       tc05::fence_before_sync();
       __syncwarp();
