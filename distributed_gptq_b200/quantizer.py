@@ -265,7 +265,9 @@ class DistributedGPTQuantizer:
                     stats = co.comm.broadcast_object(entry["stats"] if entry else None, src=src)
                     if entry is None:
                         entry = {"stats": stats, "packed": {
-                            k: torch.empty(s, dtype=d, device=co.device) for k, (s, d) in shapes.items()}}
+                            k: (layer.bias.data if k.endswith(".bias")      # not quantized: local copy
+                                else torch.empty(s, dtype=d, device=co.device))
+                            for k, (s, d) in shapes.items()}}
                         results[n] = entry
                     for k in sorted(entry["packed"]):
                         if not k.endswith(".bias"):
