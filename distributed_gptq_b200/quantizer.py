@@ -106,6 +106,10 @@ class DistributedGPTQuantizer:
         self.packed: Dict[str, Dict[str, torch.Tensor]] = {}
         self.layer_info: Dict[str, dict] = {}
         self.timings: Dict[str, float] = {}
+        # diagnostics: when set before quantize_model, the reduced raw Hessian of every layer
+        # this rank quantizes is kept (on the host) in `hessians`
+        self.keep_hessians = False
+        self.hessians: Dict[str, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ discovery
     def _find_layers_to_quantize(self, model: nn.Module) -> Dict[str, nn.Module]:
@@ -241,6 +245,8 @@ class DistributedGPTQuantizer:
                         q = quantizers[n]
                         if n != g:
                             q._Hbuf, q.nsamples = quantizers[g]._Hbuf, n_global
+                        if self.keep_hessians:
+                            self.hessians[n] = q.H.detach().cpu().clone()
                         stats = q.quantize()
                         fmt = io.file_format(cfg.bits)
                         results[n] = {"stats": stats, "packed": io.packed_state(n, q, fmt)}
