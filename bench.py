@@ -277,44 +277,46 @@ def cpu_reference_sample(scale: float = 1.0):
     """Times the CPU restatement of the reference (oracle/) on a bounded sample of the sweep
     with all host threads and extrapolates to seconds per sweep.
 
-    Sample: Hessian X^T X (fp32) at K=4096 and K=11008 on a few thousand tokens; the
-    Cholesky -> inverse -> Cholesky chain at K=4096 (scaled by K^3 for K=11008); the block /
-    column loop at K=4096 on a subset of rows (rows are independent: scaled by N_out / rows
-    and by (K/4096)^2 for K=11008).
+    Sample: Hessian X^T X (fp32) at K=4096 and K=11008 on a subset of the tokens; the
+    Cholesky -> inverse -> Cholesky chain at both K in full; the block / column loop at
+    K=4096 on a subset of rows (rows are independent: scaled by N_out / rows and by
+    (K/4096)^2 for K=11008).
     """
     from oracle import oracle_gptq as O
     torch.set_num_threads(os.cpu_count() or 1)
     cores = torch.get_num_threads()
     g = torch.Generator().manual_seed(0)
     t_all0 = time.perf_counter()
-    tok4, tok11 = int(8192 * scale), int(2048 * scale)
-    per_token = {}
+    tok4, tok11 = int(49152 * scale), int(6144 * scale)
+    per_token, H_of = {}, {}
     for K, tok in ((4096, tok4), (11008, tok11)):
-        x = torch.randn(tok, K, generator=g)
+        H, chunk = None, 2048
         t0 = time.perf_counter()
-        H, _ = O.hessian_add_batch(None, 0, x)
-        per_token[K] = (time.perf_counter() - t0) / tok
-        if K == 4096:
-            H4 = H + torch.eye(K) * float(H.diagonal().mean())
-    t0 = time.perf_counter()
-    O.damped_inv_chol(H4, PERCDAMP)
-    inv4 = time.perf_counter() - t0
-    rows = max(16, int(64 * scale))
+        for s0 in range(0, tok, chunk):
+            x = torch.randn(min(chunk, tok - s0), K, generator=g)
+            H, _ = O.hessian_add_batch(H, 0, x)
+        per_token[K] = (time.perf_counter() - t0) / tok   # includes drawing the sample
+        H_of[K] = H + torch.eye(K) * float(H.diagonal().mean())
+    inv = {}
+    for K in (4096, 11008):
+        t0 = time.perf_counter()
+        O.damped_inv_chol(H_of[K], PERCDAMP)
+        inv[K] = time.perf_counter() - t0
+    rows = max(16, int(512 * scale))
     W = torch.randn(rows, 4096, generator=g) * 0.02
     t0 = time.perf_counter()
-    O.gptq_quantize(W, H4, 4, 4, GROUP, BLOCK, PERCDAMP, True)
-    loop4 = max(time.perf_counter() - t0 - inv4, 1e-3)
+    O.gptq_quantize(W, H_of[4096], 4, 4, GROUP, BLOCK, PERCDAMP, True)
+    loop4 = max(time.perf_counter() - t0 - inv[4096], 1e-3)
     total = 0.0
     T = NSEQ * SEQ
     for _, N_out, K in LAYERS:
         hess = per_token[K] * T
-        inv = inv4 * (K / 4096) ** 3
         loop = loop4 * (N_out / rows) * (K / 4096) ** 2
-        total += len(SETTINGS) * (hess + inv + loop)
-    sample = (f"oracle port, torch fp32 CPU: X^T X on {tok4} tokens (K=4096) and {tok11} tokens "
-              f"(K=11008), Cholesky->inverse->Cholesky at K=4096, column loop on {rows} rows at "
-              f"K=4096; extrapolated linearly in tokens and rows, K^3 for the inverse chain, K^2 "
-              f"for the loop; measured {time.perf_counter() - t_all0:.1f} s of CPU work")
+        total += len(SETTINGS) * (hess + inv[K] + loop)
+    sample = (f"oracle port, torch fp32 CPU, {cores} threads: X^T X on {tok4} tokens (K=4096) and "
+              f"{tok11} tokens (K=11008), Cholesky->inverse->Cholesky at K=4096 and K=11008 in "
+              f"full, column loop on {rows} rows at K=4096; extrapolated linearly in tokens and "
+              f"rows and with K^2 for the loop; {time.perf_counter() - t_all0:.1f} s of CPU work")
     return total, cores, sample
 
 
