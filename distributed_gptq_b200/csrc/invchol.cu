@@ -12,13 +12,13 @@
 // The work is done on a reversed copy V = J A J (lower triangle, zeros above) by a
 // recursion that produces L^-1 directly, without ever storing L:
 //
-//   inv_chol(V):  split V = [V11 . ; V21 V22] at a multiple of 64
+//   inv_chol(V):  split V = [V11 . ; V21 V22] at a multiple of 128
 //     X11 = inv_chol(V11)                      (recursion; X11 = L11^-1, lower)
 //     T   = V21 * X11^T                        (= L21)
 //     V22 -= T * T^T                           (Schur complement, lower part)
 //     X22 = inv_chol(V22)                      (recursion)
 //     V21 = -X22 * (T * X11)                   (block of the inverse)
-//   leaves (<= 64 x 64) are factored and inverted by one small CTA in shared memory.
+//   leaves (<= 128 x 128) are factored and inverted by one CTA in shared memory.
 //
 // All products are independent-tile matrix products whose reduction ranges are clipped
 // to the non-zero part of the triangular operands: on the tensor cores with the
@@ -33,7 +33,7 @@
 
 namespace {
 
-constexpr int NB = 64;  // leaf size
+constexpr int NB = 128;  // leaf size: blocks of at most NB x NB are handled by one CTA
 
 // ---- reversal copies ---------------------------------------------------------------------
 // V[i][j] = (j <= i) ? A[K-1-i][K-1-j] : 0     (reads the upper triangle of A)
@@ -60,30 +60,33 @@ reverse_out_kernel(const float* __restrict__ V, int64_t ldv, float* __restrict__
 }
 
 // ---- leaf: Cholesky + inverse of one diagonal block ------------------------------------------
-// One CTA of 256 threads.  D (nb x nb, nb <= 64, lower part read) is replaced by
+// One CTA of 256 threads.  D (nb x nb, nb <= 128, lower part read) is replaced by
 // inv(chol(D)) (lower; the part above the diagonal is written as zeros).  This kernel
-// sits on the critical path K/64 times, so it is written for latency.  The block is
-// treated as 2 x 2 tiles of 32 x 32:
-//   X11 = inv(chol(A11))                one warp, rows/columns in registers (below)
-//   L21 = A21 X11^T ; A22 -= L21 L21^T  all eight warps, operands in shared memory
-//   X22 = inv(chol(A22))                one warp
-//   X21 = -X22 (L21 X11)                all eight warps
+// sits on the critical path K/128 times, so it is written for latency; the whole block
+// lives in shared memory.  It applies the same recursion as the host code, twice:
+//   128 = 2 x 64:  X11 = leaf64(A11); L21 = A21 X11^T; A22 -= L21 L21^T; X22 = leaf64(A22);
+//                  X21 = -X22 (L21 X11)                      (products: all eight warps)
+//   64  = 2 x 32:  the same with 32 x 32 tiles, whose factorisation and inverse are done by
+//                  one warp each:
 // chol32: lane i keeps row i of the tile in 32 registers, rotated so that the current
 // column always sits in register 0 (the shift is folded into the update's destination
 // register), pivots and column entries travel by warp shuffles - no barriers, no
 // dynamically indexed registers, and a rolled loop that stays in the instruction cache.
 // inv32: lane t keeps column t of the inverse the same way; the entries of L it needs are
 // the same for all lanes and are read from shared memory as broadcasts.
+constexpr int LEAF = 128;             // largest block the leaf kernel takes
 constexpr int LEAF_THREADS = 256;
-constexpr int HT = 32;  // tile edge
+constexpr int HT = 32;                // tile edge
+constexpr int LD = LEAF + 1;          // row stride of the shared-memory block (odd: no bank conflicts)
+constexpr int LD64 = 64 + 1;
 
-// L (lower, including the diagonal) of the 32 x 32 tile at S[r0.., c0..] replaces it; the
+// L (lower, including the diagonal) of the 32 x 32 tile at S[r0.., r0..] replaces it; the
 // entries above the diagonal are written as zeros.  One warp.
-__device__ __forceinline__ void chol32(float (*S)[NB + 1], float* rdiag, int r0, int lane,
-                                       int32_t* info, int pivot_base) {
+__device__ __forceinline__ void chol32(float* S, float* rdiag, int r0, int lane, int32_t* info,
+                                       int pivot_base) {
   float a[HT];
 #pragma unroll
-  for (int j = 0; j < HT; ++j) a[j] = S[r0 + lane][r0 + j];
+  for (int j = 0; j < HT; ++j) a[j] = S[(r0 + lane) * LD + r0 + j];
 #pragma unroll 1
   for (int k = 0; k < HT; ++k) {
     float d = __shfl_sync(0xffffffffu, a[0], k);
@@ -95,7 +98,7 @@ __device__ __forceinline__ void chol32(float (*S)[NB + 1], float* rdiag, int r0,
     float rs = rsqrtf(d);
     rs = rs * fmaf(-0.5f * d * rs, rs, 1.5f);   // one Newton step: 1/sqrt(d) to ~1 ulp
     const float l = (lane == k) ? d * rs : (lane > k ? a[0] * rs : 0.f);
-    S[r0 + lane][r0 + k] = l;
+    S[(r0 + lane) * LD + r0 + k] = l;
     if (lane == k) rdiag[r0 + k] = rs;   // 1 / L[k][k], reused by the inverse
     // all shuffles of the step are issued before the first dependent multiply-add, so
     // that their latencies overlap instead of adding up
@@ -110,8 +113,8 @@ __device__ __forceinline__ void chol32(float (*S)[NB + 1], float* rdiag, int r0,
 }
 
 // X[r0.., r0..] = inverse of the lower-triangular tile L = S[r0.., r0..].  One warp.
-__device__ __forceinline__ void inv32(float (*S)[NB + 1], float (*X)[NB + 1], const float* rdiag,
-                                      int r0, int lane) {
+__device__ __forceinline__ void inv32(const float* S, float* X, const float* rdiag, int r0,
+                                      int lane) {
   float y[HT];
 #pragma unroll
   for (int i = 0; i < HT; ++i) y[i] = (i == lane) ? 1.f : 0.f;
@@ -120,85 +123,139 @@ __device__ __forceinline__ void inv32(float (*S)[NB + 1], float (*X)[NB + 1], co
     // column k of L first (independent of y), then the dependent arithmetic
     float lk[HT];
 #pragma unroll
-    for (int i = 1; i < HT; ++i) lk[i] = S[r0 + min(k + i, HT - 1)][r0 + k];  // past the tile: dead
+    for (int i = 1; i < HT; ++i) lk[i] = S[(r0 + min(k + i, HT - 1)) * LD + r0 + k];  // past the tile: dead
     const float xk = y[0] * rdiag[r0 + k];                 // row k of X is final
-    X[r0 + k][r0 + lane] = xk;
+    X[(r0 + k) * LD + r0 + lane] = xk;
 #pragma unroll
     for (int i = 1; i < HT; ++i) y[i - 1] = fmaf(-lk[i], xk, y[i]);
     y[HT - 1] = 0.f;
   }
 }
 
-// C(32 x 32) = alpha * A * B (+ C0) on tiles in shared memory; element accessors are passed
-// as lambdas so that transposes cost nothing.  All 256 threads, 4 outputs each.
-template <typename FA, typename FB, typename FC>
-__device__ __forceinline__ void mm32(int tid, FA a_at, FB b_at, FC store) {
-  const int i = tid >> 3, j0 = (tid & 7) * 4;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-  for (int k = 0; k < HT; ++k) {
-    const float av = a_at(i, k);
+// C(E x E) = A * B on tiles in shared memory, E = 32 or 64; element accessors are passed as
+// lambdas so that transposes and offsets cost nothing.  All 256 threads.
+template <int E, typename FA, typename FB, typename FC>
+__device__ __forceinline__ void mm_tile(int tid, FA a_at, FB b_at, FC store) {
+  constexpr int RM = (E == 64) ? 4 : 1, RN = 4;          // outputs per thread
+  const int i0 = (tid / (E / RN)) * RM, j0 = (tid % (E / RN)) * RN;
+  float acc[RM][RN];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[e] = fmaf(av, b_at(k, j0 + e), acc[e]);
+  for (int a = 0; a < RM; ++a)
+#pragma unroll
+    for (int b = 0; b < RN; ++b) acc[a][b] = 0.f;
+#pragma unroll 4
+  for (int k = 0; k < E; ++k) {
+    float av[RM], bv[RN];
+#pragma unroll
+    for (int a = 0; a < RM; ++a) av[a] = a_at(i0 + a, k);
+#pragma unroll
+    for (int b = 0; b < RN; ++b) bv[b] = b_at(k, j0 + b);
+#pragma unroll
+    for (int a = 0; a < RM; ++a)
+#pragma unroll
+      for (int b = 0; b < RN; ++b) acc[a][b] = fmaf(av[a], bv[b], acc[a][b]);
   }
 #pragma unroll
-  for (int e = 0; e < 4; ++e) store(i, j0 + e, acc[e]);
+  for (int a = 0; a < RM; ++a)
+#pragma unroll
+    for (int b = 0; b < RN; ++b) store(i0 + a, j0 + b, acc[a][b]);
 }
 
-__global__ void __launch_bounds__(LEAF_THREADS)
-leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
-  __shared__ float S[NB][NB + 1];
-  __shared__ float X[NB][NB + 1];
-  __shared__ float T1[HT][HT + 1];
-  __shared__ float T2[HT][HT + 1];
-  __shared__ float rdiag[NB];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  {
-    // all of a thread's global loads are issued before the first store to shared memory
-    float v[NB * NB / LEAF_THREADS];
-#pragma unroll
-    for (int e = 0; e < NB * NB / LEAF_THREADS; ++e) {
-      const int idx = tid + e * LEAF_THREADS, i = idx / NB, j = idx % NB;
-      v[e] = (i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f) : (i == j ? 1.f : 0.f);
-    }
-#pragma unroll
-    for (int e = 0; e < NB * NB / LEAF_THREADS; ++e) {
-      const int idx = tid + e * LEAF_THREADS, i = idx / NB, j = idx % NB;
-      S[i][j] = v[e];
-      X[i][j] = 0.f;
-    }
-  }
-  __syncthreads();
+// inv(chol()) of the 64 x 64 block at S[o.., o..] into X[o.., o..].  Whole CTA; T32a/T32b are
+// two 32 x 33 scratch tiles.
+__device__ __forceinline__ void leaf64(float* S, float* X, float* rdiag, float* T32a, float* T32b,
+                                       int o, int tid, int32_t* info, int pivot_base) {
+  const int lane = tid & 31, warp = tid >> 5;
+  constexpr int TL = HT + 1;
   if (warp == 0) {
-    chol32(S, rdiag, 0, lane, info, pivot_base);
+    chol32(S, rdiag, o, lane, info, pivot_base);
     __syncwarp();
-    inv32(S, X, rdiag, 0, lane);
+    inv32(S, X, rdiag, o, lane);
   }
   __syncthreads();
   // L21 = A21 * X11^T
-  mm32(tid, [&](int i, int k) { return S[HT + i][k]; }, [&](int k, int j) { return X[j][k]; },
-       [&](int i, int j, float v) { T1[i][j] = v; });
+  mm_tile<HT>(tid, [&](int i, int k) { return S[(o + HT + i) * LD + o + k]; },
+              [&](int k, int j) { return X[(o + j) * LD + o + k]; },
+              [&](int i, int j, float v) { T32a[i * TL + j] = v; });
   __syncthreads();
   // A22 -= L21 * L21^T
-  mm32(tid, [&](int i, int k) { return T1[i][k]; }, [&](int k, int j) { return T1[j][k]; },
-       [&](int i, int j, float v) { S[HT + i][HT + j] -= v; });
+  mm_tile<HT>(tid, [&](int i, int k) { return T32a[i * TL + k]; },
+              [&](int k, int j) { return T32a[j * TL + k]; },
+              [&](int i, int j, float v) { S[(o + HT + i) * LD + o + HT + j] -= v; });
   __syncthreads();
   if (warp == 0) {
-    chol32(S, rdiag, HT, lane, info, pivot_base - HT);
+    chol32(S, rdiag, o + HT, lane, info, pivot_base - HT);
     __syncwarp();
-    inv32(S, X, rdiag, HT, lane);
+    inv32(S, X, rdiag, o + HT, lane);
   }
   __syncthreads();
-  // T2 = L21 * X11 ;  X21 = -X22 * T2
-  mm32(tid, [&](int i, int k) { return T1[i][k]; }, [&](int k, int j) { return X[k][j]; },
-       [&](int i, int j, float v) { T2[i][j] = v; });
+  // T = L21 * X11 ;  X21 = -X22 * T
+  mm_tile<HT>(tid, [&](int i, int k) { return T32a[i * TL + k]; },
+              [&](int k, int j) { return X[(o + k) * LD + o + j]; },
+              [&](int i, int j, float v) { T32b[i * TL + j] = v; });
   __syncthreads();
-  mm32(tid, [&](int i, int k) { return X[HT + i][HT + k]; }, [&](int k, int j) { return T2[k][j]; },
-       [&](int i, int j, float v) { X[HT + i][j] = -v; });
+  mm_tile<HT>(tid, [&](int i, int k) { return X[(o + HT + i) * LD + o + HT + k]; },
+              [&](int k, int j) { return T32b[k * TL + j]; },
+              [&](int i, int j, float v) { X[(o + HT + i) * LD + o + j] = -v; });
   __syncthreads();
-  for (int idx = tid; idx < NB * NB; idx += LEAF_THREADS) {
-    const int i = idx / NB, j = idx % NB;
-    if (i < nb && j < nb) D[(int64_t)i * ldd + j] = X[i][j];
+}
+
+constexpr size_t LEAF_SMEM_FLOATS = 2 * (size_t)LEAF * LD + 2 * 64 * LD64 + 2 * HT * (HT + 1) + LEAF;
+
+__global__ void __launch_bounds__(LEAF_THREADS)
+leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
+  extern __shared__ float leaf_smem[];
+  float* S = leaf_smem;                      // [LEAF][LD]   the block, then its Cholesky factor
+  float* X = S + LEAF * LD;                  // [LEAF][LD]   the inverse factor
+  float* T1 = X + LEAF * LD;                 // [64][LD64]   L21 of the 128-level
+  float* T2 = T1 + 64 * LD64;                // [64][LD64]
+  float* T32a = T2 + 64 * LD64;              // [32][33]
+  float* T32b = T32a + HT * (HT + 1);
+  float* rdiag = T32b + HT * (HT + 1);       // [LEAF]
+  const int tid = threadIdx.x;
+  const int span = nb <= 64 ? 64 : LEAF;     // a block of at most 64 skips the 128-level
+  for (int idx0 = tid; idx0 < span * span; idx0 += LEAF_THREADS * 8) {
+    // a batch of global loads is issued before the first store to shared memory
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int idx = idx0 + e * LEAF_THREADS, i = idx / span, j = idx % span;
+      v[e] = (idx < span * span && i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f)
+                                                      : (i == j ? 1.f : 0.f);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int idx = idx0 + e * LEAF_THREADS, i = idx / span, j = idx % span;
+      if (idx < span * span) { S[i * LD + j] = v[e]; X[i * LD + j] = 0.f; }
+    }
+  }
+  __syncthreads();
+  leaf64(S, X, rdiag, T32a, T32b, 0, tid, info, pivot_base);
+  if (span == LEAF) {
+    // L21 = A21 * X11^T
+    mm_tile<64>(tid, [&](int i, int k) { return S[(64 + i) * LD + k]; },
+                [&](int k, int j) { return X[j * LD + k]; },
+                [&](int i, int j, float v) { T1[i * LD64 + j] = v; });
+    __syncthreads();
+    // A22 -= L21 * L21^T
+    mm_tile<64>(tid, [&](int i, int k) { return T1[i * LD64 + k]; },
+                [&](int k, int j) { return T1[j * LD64 + k]; },
+                [&](int i, int j, float v) { S[(64 + i) * LD + 64 + j] -= v; });
+    __syncthreads();
+    leaf64(S, X, rdiag, T32a, T32b, 64, tid, info, pivot_base - 64);
+    // T2 = L21 * X11 ;  X21 = -X22 * T2
+    mm_tile<64>(tid, [&](int i, int k) { return T1[i * LD64 + k]; },
+                [&](int k, int j) { return X[k * LD + j]; },
+                [&](int i, int j, float v) { T2[i * LD64 + j] = v; });
+    __syncthreads();
+    mm_tile<64>(tid, [&](int i, int k) { return X[(64 + i) * LD + 64 + k]; },
+                [&](int k, int j) { return T2[k * LD64 + j]; },
+                [&](int i, int j, float v) { X[(64 + i) * LD + j] = -v; });
+    __syncthreads();
+  }
+  for (int idx = tid; idx < nb * nb; idx += LEAF_THREADS) {
+    const int i = idx / nb, j = idx % nb;
+    D[(int64_t)i * ldd + j] = X[i * LD + j];
   }
 }
 
@@ -251,7 +308,8 @@ void rec(Plan& p, int o, int n, int depth) {
   float* V = p.V;
   const int64_t ld = p.ldv;
   if (n <= NB) {
-    leaf_inv_chol_kernel<<<1, LEAF_THREADS, 0, p.st>>>(V + (int64_t)o * ld + o, ld, n, p.info, p.K - 1 - o);
+    leaf_inv_chol_kernel<<<1, LEAF_THREADS, LEAF_SMEM_FLOATS * sizeof(float), p.st>>>(
+        V + (int64_t)o * ld + o, ld, n, p.info, p.K - 1 - o);
     ++p.leaves;
     return;
   }
@@ -291,6 +349,13 @@ DGQ_EXPORT int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t*
   DGQ_REQUIRE(A && ws && K > 0 && lda >= K, DGQ_ERR_ARG);
   DGQ_REQUIRE(ws_bytes >= dgq_inv_chol_workspace_bytes(K), DGQ_ERR_WORKSPACE);
   DGQ_REQUIRE(dgq_aligned(A, 16) && dgq_aligned(ws, 16), DGQ_ERR_ALIGN);
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(leaf_inv_chol_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(LEAF_SMEM_FLOATS * sizeof(float))) != cudaSuccess)
+      return DGQ_ERR_LAUNCH;
+    attr_set = true;
+  }
   Plan p;
   p.st = dgq_stream(stream);
   p.K = K;
