@@ -136,8 +136,9 @@ rtn_dequantize_kernel(const uint8_t* __restrict__ q, int64_t n, int group_size,
 // ---- act-order ---------------------------------------------------------------------
 // rank(i) = #{ j : d[j] > d[i]  or  (d[j] == d[i] and j < i) } is the position of i in
 // a stable descending sort.  The key is the prepared diagonal: d = scale*H_ii, with a
-// zero entry (dead column) replaced by 1, exactly what the damping step will see.  K <= ~16K, so the K^2 comparisons are spread over the
-// grid with the diagonal staged through shared memory.
+// zero entry (dead column) replaced by 1, exactly what the damping step will see.
+// K <= ~16K, so the K^2 comparisons are spread over the grid with the diagonal staged
+// through shared memory.
 __global__ void __launch_bounds__(256)
 actorder_rank_kernel(const float* __restrict__ H, int64_t ldh, int K, float scale,
                      int32_t* __restrict__ perm, int32_t* __restrict__ invperm) {

@@ -80,15 +80,14 @@ constexpr int HT = 32;                // tile edge
 constexpr int LD = LEAF + 1;          // row stride of the shared-memory block (odd: no bank conflicts)
 constexpr int LD64 = 64 + 1;
 
-// L (lower, including the diagonal) of the 32 x 32 tile at S[r0.., r0..] replaces it; the
-// entries above the diagonal are written as zeros.  One warp.
-__device__ __forceinline__ void chol32(float* S, float* rdiag, int r0, int lane, int32_t* info,
-                                       int pivot_base) {
-  float a[HT];
-#pragma unroll
-  for (int j = 0; j < HT; ++j) a[j] = S[(r0 + lane) * LD + r0 + j];
+// Eight consecutive steps k0 .. k0+7 of the factorisation with W live columns to the right
+// of the current one (W = 31 - k0: the rolled loop cannot shrink its body step by step, so
+// it is cut into four phases of decreasing width).
+template <int W>
+__device__ __forceinline__ void chol32_phase(float* S, float* rdiag, float (&a)[HT], int r0,
+                                             int k0, int lane, int32_t* info, int pivot_base) {
 #pragma unroll 1
-  for (int k = 0; k < HT; ++k) {
+  for (int k = k0; k < k0 + 8; ++k) {
     float d = __shfl_sync(0xffffffffu, a[0], k);
     if (!(d > 0.f) || !isfinite(d)) {
       if (lane == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
@@ -102,13 +101,43 @@ __device__ __forceinline__ void chol32(float* S, float* rdiag, int r0, int lane,
     if (lane == k) rdiag[r0 + k] = rs;   // 1 / L[k][k], reused by the inverse
     // all shuffles of the step are issued before the first dependent multiply-add, so
     // that their latencies overlap instead of adding up
-    float lj[HT];
+    float lj[W + 1];
 #pragma unroll
-    for (int j = 1; j < HT; ++j) lj[j] = __shfl_sync(0xffffffffu, l, (k + j) & (HT - 1));
+    for (int j = 1; j <= W; ++j) lj[j] = __shfl_sync(0xffffffffu, l, (k + j) & (HT - 1));
     // column k+j of the row moves from register j to register j-1 while it is updated
 #pragma unroll
-    for (int j = 1; j < HT; ++j) a[j - 1] = fmaf(-l, lj[j], a[j]);
-    a[HT - 1] = 0.f;
+    for (int j = 1; j <= W; ++j) a[j - 1] = fmaf(-l, lj[j], a[j]);
+    a[W] = 0.f;
+  }
+}
+
+// L (lower, including the diagonal) of the 32 x 32 tile at S[r0.., r0..] replaces it; the
+// entries above the diagonal are written as zeros.  One warp.
+__device__ __forceinline__ void chol32(float* S, float* rdiag, int r0, int lane, int32_t* info,
+                                       int pivot_base) {
+  float a[HT];
+#pragma unroll
+  for (int j = 0; j < HT; ++j) a[j] = S[(r0 + lane) * LD + r0 + j];
+  chol32_phase<31>(S, rdiag, a, r0, 0, lane, info, pivot_base);
+  chol32_phase<23>(S, rdiag, a, r0, 8, lane, info, pivot_base);
+  chol32_phase<15>(S, rdiag, a, r0, 16, lane, info, pivot_base);
+  chol32_phase<7>(S, rdiag, a, r0, 24, lane, info, pivot_base);
+}
+
+template <int W>
+__device__ __forceinline__ void inv32_phase(const float* S, float* X, const float* rdiag,
+                                            float (&y)[HT], int r0, int k0, int lane) {
+#pragma unroll 1
+  for (int k = k0; k < k0 + 8; ++k) {
+    // column k of L first (independent of y), then the dependent arithmetic
+    float lk[W + 1];
+#pragma unroll
+    for (int i = 1; i <= W; ++i) lk[i] = S[(r0 + min(k + i, HT - 1)) * LD + r0 + k];  // past the tile: dead
+    const float xk = y[0] * rdiag[r0 + k];                 // row k of X is final
+    X[(r0 + k) * LD + r0 + lane] = xk;
+#pragma unroll
+    for (int i = 1; i <= W; ++i) y[i - 1] = fmaf(-lk[i], xk, y[i]);
+    y[W] = 0.f;
   }
 }
 
@@ -118,18 +147,10 @@ __device__ __forceinline__ void inv32(const float* S, float* X, const float* rdi
   float y[HT];
 #pragma unroll
   for (int i = 0; i < HT; ++i) y[i] = (i == lane) ? 1.f : 0.f;
-#pragma unroll 1
-  for (int k = 0; k < HT; ++k) {
-    // column k of L first (independent of y), then the dependent arithmetic
-    float lk[HT];
-#pragma unroll
-    for (int i = 1; i < HT; ++i) lk[i] = S[(r0 + min(k + i, HT - 1)) * LD + r0 + k];  // past the tile: dead
-    const float xk = y[0] * rdiag[r0 + k];                 // row k of X is final
-    X[(r0 + k) * LD + r0 + lane] = xk;
-#pragma unroll
-    for (int i = 1; i < HT; ++i) y[i - 1] = fmaf(-lk[i], xk, y[i]);
-    y[HT - 1] = 0.f;
-  }
+  inv32_phase<31>(S, X, rdiag, y, r0, 0, lane);
+  inv32_phase<23>(S, X, rdiag, y, r0, 8, lane);
+  inv32_phase<15>(S, X, rdiag, y, r0, 16, lane);
+  inv32_phase<7>(S, X, rdiag, y, r0, 24, lane);
 }
 
 // C(E x E) = A * B on tiles in shared memory, E = 32 or 64; element accessors are passed as

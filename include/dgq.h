@@ -93,7 +93,7 @@ int32_t dgq_cast_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, voi
  * dgq_hessian_prepare: Hout[i][j] = scale * H[p(i)][p(j)]  (p = perm, or identity
  *   when perm is NULL); a zero diagonal entry becomes 1 and marks the column dead;
  *   then diag += percdamp * mean(diag).  dead_out (K bytes, in permuted order)
- *   receives the dead mask.  H and Hout must not overlap.  ws: K floats.
+ *   receives the dead mask.  H and Hout must not overlap.  ws: 256 bytes.
  * dgq_permute_cols_f32: dst[r][i] = dead && dead[i] ? 0 : src[r][perm[i]]
  * dgq_permute_cols_u8 : dst[r][i] = src[r][perm[i]]
  */
@@ -113,9 +113,10 @@ int32_t dgq_permute_cols_u8(const uint8_t* src, int64_t lds, uint8_t* dst, int64
  * Replaces core/gptq.py:121-122 (`cholesky_inverse(linalg.cholesky(H))`) and the
  * upper-Cholesky step of the GPTQ algorithm.
  *
- * In place: A (K,K) symmetric positive definite (only its lower triangle and
+ * In place: A (K,K) symmetric positive definite (only its upper triangle and
  * diagonal are read) -> U upper triangular with A^-1 = U^T U; the strict lower
- * triangle of the result is zero.  Blocked fp32 factorisation on the device.
+ * triangle of the result is zero.  Recursive blocked fp32 factorisation on the device
+ * (fp32-accurate tensor-core products above 128 x 128, one CTA per 128 x 128 leaf).
  * info (device, 2 x int32): DGQ_INFO_NOT_POSDEF and the pivot index on failure.
  * lda a multiple of 4, A 16-byte aligned.
  */
