@@ -67,216 +67,287 @@ reverse_out_kernel(const float* __restrict__ V, int64_t ldv, float* __restrict__
 //   128 = 2 x 64:  X11 = leaf64(A11); L21 = A21 X11^T; A22 -= L21 L21^T; X22 = leaf64(A22);
 //                  X21 = -X22 (L21 X11)                      (products: all eight warps)
 //   64  = 2 x 32:  the same with 32 x 32 tiles, whose factorisation and inverse are done by
-//                  one warp each:
-// chol32: lane i keeps row i of the tile in 32 registers, rotated so that the current
-// column always sits in register 0 (the shift is folded into the update's destination
-// register), pivots and column entries travel by warp shuffles - no barriers, no
-// dynamically indexed registers, and a rolled loop that stays in the instruction cache.
-// inv32: lane t keeps column t of the inverse the same way; the entries of L it needs are
-// the same for all lanes and are read from shared memory as broadcasts.
+//                  one warp each (chol32, inv32 below).
 constexpr int LEAF = 128;             // largest block the leaf kernel takes
 constexpr int LEAF_THREADS = 256;
 constexpr int HT = 32;                // tile edge
-constexpr int LD = LEAF + 1;          // row stride of the shared-memory block (odd: no bank conflicts)
-constexpr int LD64 = 64 + 1;
+// Row strides (floats) of the shared-memory matrices: multiples of 4, so that rows start on
+// 16-byte boundaries, and = 4 mod 32, so that 16-byte accesses to 8 consecutive rows at the
+// same column fall into 8 different groups of 4 banks.
+constexpr int LD = LEAF + 4;
+constexpr int LD64 = 64 + 4;
+constexpr int TL = HT + 4;
 
-// Eight consecutive steps k0 .. k0+7 of the factorisation with W live columns to the right
-// of the current one (W = 31 - k0: the rolled loop cannot shrink its body step by step, so
-// it is cut into four phases of decreasing width).
-template <int W>
-__device__ __forceinline__ void chol32_phase(float* S, float* rdiag, float (&a)[HT], int r0,
-                                             int k0, int lane, int32_t* info, int pivot_base) {
-#pragma unroll 1
-  for (int k = k0; k < k0 + 8; ++k) {
-    float d = __shfl_sync(0xffffffffu, a[0], k);
+__device__ __forceinline__ float rsqrt_newton(float d) {
+  float rs;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(rs) : "f"(d));
+  return rs * fmaf(-0.5f * d * rs, rs, 1.5f);   // one Newton step: 1/sqrt(d) to ~1 ulp
+}
+
+// Cholesky factor of the 32 x 32 tile at S[r0.., r0..] (lower part read).  The factor is
+// written transposed to LT (row k of LT = column k of L, contiguous, zeros in front of the
+// diagonal), the reciprocals of its diagonal to rdiag; S is left as it was.  One warp; one
+// copy of the code (not inlined) serves all four tiles of a 128-block.
+//
+// Lane i keeps row i of the tile in 32 registers.  Step k: every lane scales its entry of
+// column k by 1/sqrt(pivot) and stores it to LT[k][lane]; all lanes then read the part of
+// that row they need as 16-byte broadcast loads (at most 8 loads instead of 31 shuffles) and
+// update their row.  The steps are fully unrolled, so that every register index is static
+// and step k touches only the 31-k live columns.  The next pivot, A[k+1][k+1] - L[k+1][k]^2,
+// needs nothing from other lanes: lane k+1 forms it as soon as it has its own entry of
+// column k, and one shuffle hands it to the warp.  The chain from step to step is therefore
+// multiply-add -> shuffle -> reciprocal square root -> multiply, and the round trip through
+// shared memory is off it.
+__device__ __noinline__ void chol32(const float* __restrict__ S, float* __restrict__ LT,
+                                    float* __restrict__ rdiag, int r0, int lane, int32_t* info,
+                                    int pivot_base) {
+  float a[HT];
+#pragma unroll
+  for (int q = 0; q < HT / 4; ++q) {
+    const float4 v = *reinterpret_cast<const float4*>(S + (r0 + lane) * LD + r0 + 4 * q);
+    a[4 * q] = v.x; a[4 * q + 1] = v.y; a[4 * q + 2] = v.z; a[4 * q + 3] = v.w;
+  }
+  float d = __shfl_sync(0xffffffffu, a[0], 0);
+#pragma unroll
+  for (int k = 0; k < HT; ++k) {
     if (!(d > 0.f) || !isfinite(d)) {
       if (lane == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
         info[1] = pivot_base - k;
       d = 1.f;
     }
-    float rs = rsqrtf(d);
-    rs = rs * fmaf(-0.5f * d * rs, rs, 1.5f);   // one Newton step: 1/sqrt(d) to ~1 ulp
-    const float l = (lane == k) ? d * rs : (lane > k ? a[0] * rs : 0.f);
-    S[(r0 + lane) * LD + r0 + k] = l;
+    const float rs = rsqrt_newton(d);
+    const float l = (lane == k) ? d * rs : (lane > k ? a[k] * rs : 0.f);
+    LT[k * HT + lane] = l;
     if (lane == k) rdiag[r0 + k] = rs;   // 1 / L[k][k], reused by the inverse
-    // all shuffles of the step are issued before the first dependent multiply-add, so
-    // that their latencies overlap instead of adding up
-    float lj[W + 1];
+    if (k + 1 < HT) {
+      d = __shfl_sync(0xffffffffu, fmaf(-l, l, a[k + 1]), k + 1);
+      __syncwarp();
+      float lr[HT];
 #pragma unroll
-    for (int j = 1; j <= W; ++j) lj[j] = __shfl_sync(0xffffffffu, l, (k + j) & (HT - 1));
-    // column k+j of the row moves from register j to register j-1 while it is updated
+      for (int q = (k + 1) / 4; q < HT / 4; ++q) {
+        const float4 v = *reinterpret_cast<const float4*>(LT + k * HT + 4 * q);
+        lr[4 * q] = v.x; lr[4 * q + 1] = v.y; lr[4 * q + 2] = v.z; lr[4 * q + 3] = v.w;
+      }
 #pragma unroll
-    for (int j = 1; j <= W; ++j) a[j - 1] = fmaf(-l, lj[j], a[j]);
-    a[W] = 0.f;
+      for (int j = k + 1; j < HT; ++j) a[j] = fmaf(-l, lr[j], a[j]);
+    }
   }
 }
 
-// L (lower, including the diagonal) of the 32 x 32 tile at S[r0.., r0..] replaces it; the
-// entries above the diagonal are written as zeros.  One warp.
-__device__ __forceinline__ void chol32(float* S, float* rdiag, int r0, int lane, int32_t* info,
-                                       int pivot_base) {
-  float a[HT];
+// X[r0.., r0..] = inverse of the lower-triangular tile whose transpose is in LT.  One warp:
+// lane t keeps column t of the inverse in registers; the entries of L that step k needs are
+// the same for all lanes and come from row k of LT as 16-byte broadcast loads, fetched one
+// step ahead of their use.
+__device__ __noinline__ void inv32(const float* __restrict__ LT, float* __restrict__ X,
+                                   const float* __restrict__ rdiag, int r0, int lane) {
+  float y[HT], rd[HT];
 #pragma unroll
-  for (int j = 0; j < HT; ++j) a[j] = S[(r0 + lane) * LD + r0 + j];
-  chol32_phase<31>(S, rdiag, a, r0, 0, lane, info, pivot_base);
-  chol32_phase<23>(S, rdiag, a, r0, 8, lane, info, pivot_base);
-  chol32_phase<15>(S, rdiag, a, r0, 16, lane, info, pivot_base);
-  chol32_phase<7>(S, rdiag, a, r0, 24, lane, info, pivot_base);
-}
-
-template <int W>
-__device__ __forceinline__ void inv32_phase(const float* S, float* X, const float* rdiag,
-                                            float (&y)[HT], int r0, int k0, int lane) {
-#pragma unroll 1
-  for (int k = k0; k < k0 + 8; ++k) {
-    // column k of L first (independent of y), then the dependent arithmetic
-    float lk[W + 1];
-#pragma unroll
-    for (int i = 1; i <= W; ++i) lk[i] = S[(r0 + min(k + i, HT - 1)) * LD + r0 + k];  // past the tile: dead
-    const float xk = y[0] * rdiag[r0 + k];                 // row k of X is final
-    X[(r0 + k) * LD + r0 + lane] = xk;
-#pragma unroll
-    for (int i = 1; i <= W; ++i) y[i - 1] = fmaf(-lk[i], xk, y[i]);
-    y[W] = 0.f;
+  for (int q = 0; q < HT / 4; ++q) {
+    const float4 v = *reinterpret_cast<const float4*>(rdiag + r0 + 4 * q);
+    rd[4 * q] = v.x; rd[4 * q + 1] = v.y; rd[4 * q + 2] = v.z; rd[4 * q + 3] = v.w;
   }
-}
-
-// X[r0.., r0..] = inverse of the lower-triangular tile L = S[r0.., r0..].  One warp.
-__device__ __forceinline__ void inv32(const float* S, float* X, const float* rdiag, int r0,
-                                      int lane) {
-  float y[HT];
 #pragma unroll
   for (int i = 0; i < HT; ++i) y[i] = (i == lane) ? 1.f : 0.f;
-  inv32_phase<31>(S, X, rdiag, y, r0, 0, lane);
-  inv32_phase<23>(S, X, rdiag, y, r0, 8, lane);
-  inv32_phase<15>(S, X, rdiag, y, r0, 16, lane);
-  inv32_phase<7>(S, X, rdiag, y, r0, 24, lane);
+  float lr[HT], nx[HT];
+#pragma unroll
+  for (int q = 0; q < HT / 4; ++q) {
+    const float4 v = *reinterpret_cast<const float4*>(LT + 4 * q);
+    lr[4 * q] = v.x; lr[4 * q + 1] = v.y; lr[4 * q + 2] = v.z; lr[4 * q + 3] = v.w;
+  }
+#pragma unroll
+  for (int k = 0; k < HT; ++k) {
+    if (k + 2 < HT) {
+#pragma unroll
+      for (int q = (k + 2) / 4; q < HT / 4; ++q) {
+        const float4 v = *reinterpret_cast<const float4*>(LT + (k + 1) * HT + 4 * q);
+        nx[4 * q] = v.x; nx[4 * q + 1] = v.y; nx[4 * q + 2] = v.z; nx[4 * q + 3] = v.w;
+      }
+    }
+    const float xk = y[k] * rd[k];                         // row k of X is final
+    X[(r0 + k) * LD + r0 + lane] = xk;
+#pragma unroll
+    for (int i = k + 1; i < HT; ++i) y[i] = fmaf(-lr[i], xk, y[i]);
+#pragma unroll
+    for (int i = 0; i < HT; ++i) lr[i] = nx[i];
+  }
 }
 
-// C(E x E) = A * B on tiles in shared memory, E = 32 or 64; element accessors are passed as
-// lambdas so that transposes and offsets cost nothing.  All 256 threads.
-template <int E, typename FA, typename FB, typename FC>
-__device__ __forceinline__ void mm_tile(int tid, FA a_at, FB b_at, FC store) {
+// C (E x E) = A * B on tiles in shared memory, E = 32 or 64, all 256 threads.  A is given by
+// rows (A[i * lda + k]); B by rows of its transpose when !B_KN (B[j * ldb + k]), or as it is
+// when B_KN (B[k * ldb + j]).  Everything that is contiguous is read 16 bytes at a time: four
+// reduction steps of A per load, and of B either four reduction steps of one column (!B_KN;
+// the thread's columns are interleaved, g, g+E/4, .., so that the rows it reads with its
+// neighbours fall into different banks) or one step of four adjacent columns (B_KN).
+// All base addresses and strides must be multiples of 16 bytes.
+template <int E, bool B_KN, typename FC>
+__device__ __forceinline__ void mm_tile(int tid, const float* __restrict__ A, int lda,
+                                        const float* __restrict__ B, int ldb, FC store) {
   constexpr int RM = (E == 64) ? 4 : 1, RN = 4;          // outputs per thread
-  const int i0 = (tid / (E / RN)) * RM, j0 = (tid % (E / RN)) * RN;
+  constexpr int G = E / RN;                              // column groups
+  constexpr int RSTEP = LEAF_THREADS / G;                // distance between a thread's rows
+  const int g = tid % G, r = tid / G;
   float acc[RM][RN];
 #pragma unroll
   for (int a = 0; a < RM; ++a)
 #pragma unroll
     for (int b = 0; b < RN; ++b) acc[a][b] = 0.f;
-#pragma unroll 4
-  for (int k = 0; k < E; ++k) {
-    float av[RM], bv[RN];
-#pragma unroll
-    for (int a = 0; a < RM; ++a) av[a] = a_at(i0 + a, k);
-#pragma unroll
-    for (int b = 0; b < RN; ++b) bv[b] = b_at(k, j0 + b);
+#pragma unroll 2
+  for (int k = 0; k < E; k += 4) {
+    float4 av[RM];
 #pragma unroll
     for (int a = 0; a < RM; ++a)
+      av[a] = *reinterpret_cast<const float4*>(A + (r + a * RSTEP) * lda + k);
+    if (!B_KN) {
+      float4 bv[RN];
 #pragma unroll
-      for (int b = 0; b < RN; ++b) acc[a][b] = fmaf(av[a], bv[b], acc[a][b]);
+      for (int b = 0; b < RN; ++b)
+        bv[b] = *reinterpret_cast<const float4*>(B + (g + b * G) * ldb + k);
+#pragma unroll
+      for (int a = 0; a < RM; ++a)
+#pragma unroll
+        for (int b = 0; b < RN; ++b) {
+          acc[a][b] = fmaf(av[a].x, bv[b].x, acc[a][b]);
+          acc[a][b] = fmaf(av[a].y, bv[b].y, acc[a][b]);
+          acc[a][b] = fmaf(av[a].z, bv[b].z, acc[a][b]);
+          acc[a][b] = fmaf(av[a].w, bv[b].w, acc[a][b]);
+        }
+    } else {
+      float4 bk[4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        bk[kk] = *reinterpret_cast<const float4*>(B + (k + kk) * ldb + 4 * g);
+#pragma unroll
+      for (int a = 0; a < RM; ++a) {
+        const float ak[4] = {av[a].x, av[a].y, av[a].z, av[a].w};
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          acc[a][0] = fmaf(ak[kk], bk[kk].x, acc[a][0]);
+          acc[a][1] = fmaf(ak[kk], bk[kk].y, acc[a][1]);
+          acc[a][2] = fmaf(ak[kk], bk[kk].z, acc[a][2]);
+          acc[a][3] = fmaf(ak[kk], bk[kk].w, acc[a][3]);
+        }
+      }
+    }
   }
 #pragma unroll
   for (int a = 0; a < RM; ++a)
 #pragma unroll
-    for (int b = 0; b < RN; ++b) store(i0 + a, j0 + b, acc[a][b]);
+    for (int b = 0; b < RN; ++b)
+      store(r + a * RSTEP, B_KN ? 4 * g + b : g + b * G, acc[a][b]);
 }
 
 // inv(chol()) of the 64 x 64 block at S[o.., o..] into X[o.., o..].  Whole CTA; T32a/T32b are
-// two 32 x 33 scratch tiles.
+// two 32 x TL scratch tiles, LT a 32 x 32 one.
 __device__ __forceinline__ void leaf64(float* S, float* X, float* rdiag, float* T32a, float* T32b,
-                                       int o, int tid, int32_t* info, int pivot_base) {
+                                       float* LT, int o, int tid, int32_t* info, int pivot_base) {
   const int lane = tid & 31, warp = tid >> 5;
-  constexpr int TL = HT + 1;
+  float* S21 = S + (o + HT) * LD + o;
+  float* S22 = S21 + HT;
+  float* X11 = X + o * LD + o;
+  float* X21 = X + (o + HT) * LD + o;
+  float* X22 = X21 + HT;
   if (warp == 0) {
-    chol32(S, rdiag, o, lane, info, pivot_base);
+    chol32(S, LT, rdiag, o, lane, info, pivot_base);
     __syncwarp();
-    inv32(S, X, rdiag, o, lane);
+    inv32(LT, X, rdiag, o, lane);
   }
   __syncthreads();
   // L21 = A21 * X11^T
-  mm_tile<HT>(tid, [&](int i, int k) { return S[(o + HT + i) * LD + o + k]; },
-              [&](int k, int j) { return X[(o + j) * LD + o + k]; },
-              [&](int i, int j, float v) { T32a[i * TL + j] = v; });
+  mm_tile<HT, false>(tid, S21, LD, X11, LD, [&](int i, int j, float v) { T32a[i * TL + j] = v; });
   __syncthreads();
   // A22 -= L21 * L21^T
-  mm_tile<HT>(tid, [&](int i, int k) { return T32a[i * TL + k]; },
-              [&](int k, int j) { return T32a[j * TL + k]; },
-              [&](int i, int j, float v) { S[(o + HT + i) * LD + o + HT + j] -= v; });
+  mm_tile<HT, false>(tid, T32a, TL, T32a, TL, [&](int i, int j, float v) { S22[i * LD + j] -= v; });
   __syncthreads();
   if (warp == 0) {
-    chol32(S, rdiag, o + HT, lane, info, pivot_base - HT);
+    chol32(S, LT, rdiag, o + HT, lane, info, pivot_base - HT);
     __syncwarp();
-    inv32(S, X, rdiag, o + HT, lane);
+    inv32(LT, X, rdiag, o + HT, lane);
   }
   __syncthreads();
   // T = L21 * X11 ;  X21 = -X22 * T
-  mm_tile<HT>(tid, [&](int i, int k) { return T32a[i * TL + k]; },
-              [&](int k, int j) { return X[(o + k) * LD + o + j]; },
-              [&](int i, int j, float v) { T32b[i * TL + j] = v; });
+  mm_tile<HT, true>(tid, T32a, TL, X11, LD, [&](int i, int j, float v) { T32b[i * TL + j] = v; });
   __syncthreads();
-  mm_tile<HT>(tid, [&](int i, int k) { return X[(o + HT + i) * LD + o + HT + k]; },
-              [&](int k, int j) { return T32b[k * TL + j]; },
-              [&](int i, int j, float v) { X[(o + HT + i) * LD + o + j] = -v; });
+  mm_tile<HT, true>(tid, X22, LD, T32b, TL, [&](int i, int j, float v) { X21[i * LD + j] = -v; });
   __syncthreads();
 }
 
-constexpr size_t LEAF_SMEM_FLOATS = 2 * (size_t)LEAF * LD + 2 * 64 * LD64 + 2 * HT * (HT + 1) + LEAF;
+constexpr size_t LEAF_SMEM_FLOATS =
+    2 * (size_t)LEAF * LD + 2 * 64 * LD64 + 2 * HT * TL + LEAF + HT * HT;
 
 __global__ void __launch_bounds__(LEAF_THREADS)
 leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, int pivot_base) {
-  extern __shared__ float leaf_smem[];
-  float* S = leaf_smem;                      // [LEAF][LD]   the block, then its Cholesky factor
+  extern __shared__ __align__(16) float leaf_smem[];
+  float* S = leaf_smem;                      // [LEAF][LD]   the block, updated as the levels proceed
   float* X = S + LEAF * LD;                  // [LEAF][LD]   the inverse factor
   float* T1 = X + LEAF * LD;                 // [64][LD64]   L21 of the 128-level
   float* T2 = T1 + 64 * LD64;                // [64][LD64]
-  float* T32a = T2 + 64 * LD64;              // [32][33]
-  float* T32b = T32a + HT * (HT + 1);
-  float* rdiag = T32b + HT * (HT + 1);       // [LEAF]
+  float* T32a = T2 + 64 * LD64;              // [32][TL]
+  float* T32b = T32a + HT * TL;
+  float* rdiag = T32b + HT * TL;             // [LEAF]
+  float* LT = rdiag + LEAF;                  // [32][32]     transpose of the current 32 x 32 factor
   const int tid = threadIdx.x;
   const int span = nb <= 64 ? 64 : LEAF;     // a block of at most 64 skips the 128-level
-  for (int idx0 = tid; idx0 < span * span; idx0 += LEAF_THREADS * 8) {
-    // a batch of global loads is issued before the first store to shared memory
-    float v[8];
+  const bool vec = nb == LEAF && (ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0;
+  if (vec) {
+    // full block: every thread has all its sixteen 16-byte loads in flight at once
+    constexpr int PER = LEAF * LEAF / 4 / LEAF_THREADS;
+    float4 v[PER];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int idx = idx0 + e * LEAF_THREADS, i = idx / span, j = idx % span;
-      v[e] = (idx < span * span && i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f)
-                                                      : (i == j ? 1.f : 0.f);
+    for (int e = 0; e < PER; ++e) {
+      const int idx = tid + e * LEAF_THREADS, i = idx / (LEAF / 4), c = (idx % (LEAF / 4)) * 4;
+      v[e] = c <= i ? *reinterpret_cast<const float4*>(D + (int64_t)i * ldd + c)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int idx = idx0 + e * LEAF_THREADS, i = idx / span, j = idx % span;
-      if (idx < span * span) { S[i * LD + j] = v[e]; X[i * LD + j] = 0.f; }
+    for (int e = 0; e < PER; ++e) {
+      const int idx = tid + e * LEAF_THREADS, i = idx / (LEAF / 4), c = (idx % (LEAF / 4)) * 4;
+      float4 w = v[e];
+      if (c + 1 > i) w.y = 0.f;
+      if (c + 2 > i) w.z = 0.f;
+      if (c + 3 > i) w.w = 0.f;
+      *reinterpret_cast<float4*>(S + i * LD + c) = w;
+      *reinterpret_cast<float4*>(X + i * LD + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  } else {
+    for (int idx = tid; idx < span * span; idx += LEAF_THREADS) {
+      const int i = idx / span, j = idx % span;
+      S[i * LD + j] = (i < nb && j < nb) ? (j <= i ? D[(int64_t)i * ldd + j] : 0.f)
+                                         : (i == j ? 1.f : 0.f);
+      X[i * LD + j] = 0.f;
     }
   }
   __syncthreads();
-  leaf64(S, X, rdiag, T32a, T32b, 0, tid, info, pivot_base);
+  leaf64(S, X, rdiag, T32a, T32b, LT, 0, tid, info, pivot_base);
   if (span == LEAF) {
+    float* S21 = S + 64 * LD;
+    float* S22 = S21 + 64;
+    float* X21 = X + 64 * LD;
+    float* X22 = X21 + 64;
     // L21 = A21 * X11^T
-    mm_tile<64>(tid, [&](int i, int k) { return S[(64 + i) * LD + k]; },
-                [&](int k, int j) { return X[j * LD + k]; },
-                [&](int i, int j, float v) { T1[i * LD64 + j] = v; });
+    mm_tile<64, false>(tid, S21, LD, X, LD, [&](int i, int j, float v) { T1[i * LD64 + j] = v; });
     __syncthreads();
     // A22 -= L21 * L21^T
-    mm_tile<64>(tid, [&](int i, int k) { return T1[i * LD64 + k]; },
-                [&](int k, int j) { return T1[j * LD64 + k]; },
-                [&](int i, int j, float v) { S[(64 + i) * LD + 64 + j] -= v; });
+    mm_tile<64, false>(tid, T1, LD64, T1, LD64, [&](int i, int j, float v) { S22[i * LD + j] -= v; });
     __syncthreads();
-    leaf64(S, X, rdiag, T32a, T32b, 64, tid, info, pivot_base - 64);
+    leaf64(S, X, rdiag, T32a, T32b, LT, 64, tid, info, pivot_base - 64);
     // T2 = L21 * X11 ;  X21 = -X22 * T2
-    mm_tile<64>(tid, [&](int i, int k) { return T1[i * LD64 + k]; },
-                [&](int k, int j) { return X[k * LD + j]; },
-                [&](int i, int j, float v) { T2[i * LD64 + j] = v; });
+    mm_tile<64, true>(tid, T1, LD64, X, LD, [&](int i, int j, float v) { T2[i * LD64 + j] = v; });
     __syncthreads();
-    mm_tile<64>(tid, [&](int i, int k) { return X[(64 + i) * LD + 64 + k]; },
-                [&](int k, int j) { return T2[k * LD64 + j]; },
-                [&](int i, int j, float v) { X[(64 + i) * LD + j] = -v; });
+    mm_tile<64, true>(tid, X22, LD, T2, LD64, [&](int i, int j, float v) { X21[i * LD + j] = -v; });
     __syncthreads();
   }
-  for (int idx = tid; idx < nb * nb; idx += LEAF_THREADS) {
-    const int i = idx / nb, j = idx % nb;
-    D[(int64_t)i * ldd + j] = X[i * LD + j];
+  if (vec) {
+#pragma unroll 4
+    for (int idx = tid; idx < LEAF * LEAF / 4; idx += LEAF_THREADS) {
+      const int i = idx / (LEAF / 4), c = (idx % (LEAF / 4)) * 4;
+      *reinterpret_cast<float4*>(D + (int64_t)i * ldd + c) =
+          *reinterpret_cast<const float4*>(X + i * LD + c);
+    }
+  } else {
+    for (int idx = tid; idx < nb * nb; idx += LEAF_THREADS) {
+      const int i = idx / nb, j = idx % nb;
+      D[(int64_t)i * ldd + j] = X[i * LD + j];
+    }
   }
 }
 
