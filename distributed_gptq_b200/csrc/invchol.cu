@@ -17,7 +17,8 @@
 //     T   = V21 * X11^T                        (= L21)
 //     V22 -= T * T^T                           (Schur complement, lower part)
 //     X22 = inv_chol(V22)                      (recursion)
-//     V21 = -X22 * (T * X11)                   (block of the inverse)
+//     V21 = -X22 * (T * X11)                   (block of the inverse; T * X11 is formed on a
+//                                               side stream beside the two steps before)
 //   leaves (<= 128 x 128) are factored and inverted by one CTA in shared memory.
 //
 // All products are independent-tile matrix products whose reduction ranges are clipped
@@ -355,45 +356,71 @@ leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, 
 struct Plan {
   float* V; int64_t ldv; int K;
   float* T1[32];        // per recursion depth: the L21 block of the node being processed
-  float* T2;            // transient product T * X11
+  float* T2[32];        // per recursion depth: the product T1 * X11
   int32_t* info;
-  cudaStream_t st;
+  cudaStream_t st;      // the caller's stream
+  cudaStream_t side;    // takes T2 = T1 * X11, which nothing needs before the node's last product
+  cudaEvent_t* fork;    // per depth: T1 is ready (recorded on st)
+  cudaEvent_t* join;    // per depth: T2 is ready (recorded on side)
   int64_t leaves;
   bool use_tensor;
 };
+
+// One side stream and one pair of events per recursion depth, per host thread and device,
+// created on first use and kept for the life of the thread.
+struct SideResources {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork[32] = {}, join[32] = {};
+  bool ok = false;
+};
+SideResources* side_resources() {
+  thread_local SideResources per_device[16];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  SideResources& r = per_device[dev];
+  if (!r.ok) {
+    if (cudaStreamCreateWithFlags(&r.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    for (int d = 0; d < 32; ++d) {
+      if (cudaEventCreateWithFlags(&r.fork[d], cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&r.join[d], cudaEventDisableTiming) != cudaSuccess)
+        return nullptr;
+    }
+    r.ok = true;
+  }
+  return &r;
+}
 
 int split_point(int n) {
   const int blocks = (n + NB - 1) / NB;
   return (blocks / 2) * NB;  // first half gets floor(blocks/2) leaves (>= 1 when n > NB)
 }
 
-void rec_workspace(int n, int depth, std::vector<int64_t>& need, int64_t& t2) {
+void rec_workspace(int n, int depth, std::vector<int64_t>& need) {
   if (n <= NB) return;
   const int h = split_point(n), m2 = n - h;
   if ((int)need.size() <= depth) need.resize(depth + 1, 0);
   need[depth] = std::max<int64_t>(need[depth], (int64_t)m2 * h);
-  t2 = std::max<int64_t>(t2, (int64_t)m2 * h);
-  rec_workspace(h, depth + 1, need, t2);
-  rec_workspace(m2, depth + 1, need, t2);
+  rec_workspace(h, depth + 1, need);
+  rec_workspace(m2, depth + 1, need);
 }
 
 // One product of the recursion.  B is (n, k) row-major when !b_is_kn, (k, n) when b_is_kn.
-void mm(Plan& p, const float* a, int64_t lda, const float* b, int64_t ldb, bool b_is_kn, float* c,
-        int64_t ldc, int m, int n, int k, float alpha, float beta, int lo_from_j, int hi_from_j,
-        int hi_from_i, int lower_only) {
+void mm(Plan& p, cudaStream_t st, const float* a, int64_t lda, const float* b, int64_t ldb,
+        bool b_is_kn, float* c, int64_t ldc, int m, int n, int k, float alpha, float beta,
+        int lo_from_j, int hi_from_j, int hi_from_i, int lower_only) {
   if (p.use_tensor && m >= dgq::TGEMM_TILE && n >= dgq::TGEMM_TILE) {
     dgq::TGemmArgs t;
     t.a = a; t.lda = lda; t.b = b; t.ldb = ldb; t.c = c; t.ldc = ldc;
     t.m = m; t.n = n; t.k = k; t.alpha = alpha; t.beta = beta; t.b_is_kn = b_is_kn ? 1 : 0;
     t.lo_from_j = lo_from_j; t.hi_from_j = hi_from_j; t.hi_from_i = hi_from_i;
     t.lower_only = lower_only; t.info = p.info;
-    if (dgq::tgemm_supported(t) && dgq::tgemm_launch(t, p.st)) return;
+    if (dgq::tgemm_supported(t) && dgq::tgemm_launch(t, st)) return;
   }
   GemmArgs g = b_is_kn ? gemm_args(a, lda, 1, b, ldb, 1, c, ldc, 1, m, n, k, alpha, beta)
                        : gemm_args(a, lda, 1, b, 1, ldb, c, ldc, 1, m, n, k, alpha, beta);
   g.lo_from_j = lo_from_j; g.hi_from_j = hi_from_j; g.hi_from_i = hi_from_i;
   g.lower_only = lower_only;
-  launch_gemm(g, p.st);
+  launch_gemm(g, st);
 }
 
 void rec(Plan& p, int o, int n, int depth) {
@@ -410,16 +437,22 @@ void rec(Plan& p, int o, int n, int depth) {
   float* V21 = V + (int64_t)(o + h) * ld + o;
   float* V22 = V + (int64_t)(o + h) * ld + (o + h);
   float* T1 = p.T1[depth];
+  float* T2 = p.T2[depth];
   rec(p, o, h, depth + 1);
   // T1 = V21 * X11^T : X11[j][k] is non-zero for k <= j
-  mm(p, V21, ld, V11, ld, false, T1, h, m2, h, h, 1.f, 0.f, 0, 1, 0, 0);
+  mm(p, p.st, V21, ld, V11, ld, false, T1, h, m2, h, h, 1.f, 0.f, 0, 1, 0, 0);
+  // T2 = T1 * X11 (X11[k][j] is non-zero for k >= j) runs beside the Schur complement and
+  // the whole second half of the recursion
+  cudaEventRecord(p.fork[depth], p.st);
+  cudaStreamWaitEvent(p.side, p.fork[depth], 0);
+  mm(p, p.side, T1, h, V11, ld, true, T2, h, m2, h, h, 1.f, 0.f, 1, 0, 0, 0);
+  cudaEventRecord(p.join[depth], p.side);
   // V22 -= T1 * T1^T, lower part
-  mm(p, T1, h, T1, h, false, V22, ld, m2, m2, h, -1.f, 1.f, 0, 0, 0, 1);
+  mm(p, p.st, T1, h, T1, h, false, V22, ld, m2, m2, h, -1.f, 1.f, 0, 0, 0, 1);
   rec(p, o + h, m2, depth + 1);
-  // T2 = T1 * X11 : X11[k][j] is non-zero for k >= j
-  mm(p, T1, h, V11, ld, true, p.T2, h, m2, h, h, 1.f, 0.f, 1, 0, 0, 0);
   // V21 = -X22 * T2 : X22[i][k] is non-zero for k <= i
-  mm(p, V22, ld, p.T2, h, true, V21, ld, m2, h, m2, -1.f, 0.f, 0, 0, 1, 0);
+  cudaStreamWaitEvent(p.st, p.join[depth], 0);
+  mm(p, p.st, V22, ld, T2, h, true, V21, ld, m2, h, m2, -1.f, 0.f, 0, 0, 1, 0);
 }
 
 int64_t round4(int64_t x) { return (x + 3) / 4 * 4; }
@@ -429,10 +462,9 @@ int64_t round4(int64_t x) { return (x + 3) / 4 * 4; }
 DGQ_EXPORT int64_t dgq_inv_chol_workspace_bytes(int32_t K) {
   if (K <= 0) return DGQ_ERR_ARG;
   std::vector<int64_t> need;
-  int64_t t2 = 0;
-  rec_workspace(K, 0, need, t2);
-  int64_t floats = (int64_t)K * round4(K) + round4(t2);
-  for (int64_t v : need) floats += round4(v);
+  rec_workspace(K, 0, need);
+  int64_t floats = (int64_t)K * round4(K);
+  for (int64_t v : need) floats += 2 * round4(v);
   return (floats + 4) * (int64_t)sizeof(float);
 }
 
@@ -459,15 +491,19 @@ DGQ_EXPORT int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t*
   p.V = w;
   w += (int64_t)K * p.ldv;
   std::vector<int64_t> need;
-  int64_t t2 = 0;
-  rec_workspace(K, 0, need, t2);
+  rec_workspace(K, 0, need);
   DGQ_REQUIRE(need.size() <= 32, DGQ_ERR_SIZE);
-  p.T2 = w;
-  w += round4(t2);
   for (size_t d = 0; d < need.size(); ++d) {
     p.T1[d] = w;
     w += round4(need[d]);
+    p.T2[d] = w;
+    w += round4(need[d]);
   }
+  SideResources* side = side_resources();
+  DGQ_REQUIRE(side != nullptr, DGQ_ERR_LAUNCH);
+  p.side = side->stream;
+  p.fork = side->fork;
+  p.join = side->join;
   const unsigned grid = dgq_grid((int64_t)K * K, 256);
   reverse_in_kernel<<<grid, 256, 0, p.st>>>(A, lda, p.V, p.ldv, K);
   rec(p, 0, K, 0);

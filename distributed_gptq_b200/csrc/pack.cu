@@ -299,35 +299,44 @@ unpack_dequant_kernel(const uint8_t* __restrict__ packed, const PT* __restrict__
 // The matrix is walked as a flat array of 32-bit words (8 codes each).  A thread handles
 // four words that are 32 words apart, so that every load instruction of a warp reads 128
 // consecutive bytes and every store instruction writes 512 (bf16/fp16) or 1024 (fp32)
-// consecutive bytes; the four independent loads are in flight together.
+// consecutive bytes; the four independent loads are in flight together.  The kernel has to
+// stay below about 60 instructions per word to remain bound by HBM, so the row and column of
+// a word come from one 32-bit division per thread and step (the other three words follow by
+// addition), the group from a shift when the group size is a power of two, and the codes
+// become floats by the 2^23 trick on the FMA pipe instead of the conversion unit.
 template <typename PT, typename OT>
 __global__ void __launch_bounds__(256)
 unpack_dequant_wide4_kernel(const uint32_t* __restrict__ packed, const PT* __restrict__ scales,
-                            const PT* __restrict__ zeros, OT* __restrict__ out, int64_t n_words,
-                            int words_per_row, int n_groups, int group_size) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp_global = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t base = warp_global * 128; base < n_words; base += n_warps * 128) {
+                            const PT* __restrict__ zeros, OT* __restrict__ out, uint32_t n_words,
+                            uint32_t words_per_row, int n_groups, uint32_t group_words,
+                            int group_shift) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+  for (uint64_t base64 = (uint64_t)warp_global * 128; base64 < n_words; base64 += (uint64_t)n_warps * 128) {
+    const uint32_t base = (uint32_t)base64;
     uint32_t w[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const int64_t wi = base + q * 32 + lane;
+      const uint32_t wi = base + q * 32 + lane;
       w[q] = wi < n_words ? __ldg(packed + wi) : 0u;
     }
+    uint32_t r = (base + lane) / words_per_row;
+    uint32_t c = (base + lane) - r * words_per_row;     // word within the row
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const int64_t wi = base + q * 32 + lane;
-      if (wi >= n_words) continue;
-      const int64_t r = wi / words_per_row;
-      const int c0 = (int)(wi - r * words_per_row) * 8;
-      const int g = n_groups == 1 ? 0 : c0 / group_size;
-      const float s = dgq_to_float<PT>(scales[r * n_groups + g]);
-      const float z = dgq_to_float<PT>(zeros[r * n_groups + g]);
+      const uint32_t wi = base + q * 32 + lane;
+      if (wi >= n_words) break;
+      const uint32_t g = n_groups == 1 ? 0u : (group_shift >= 0 ? c >> group_shift : c / group_words);
+      const float s = dgq_to_float<PT>(scales[(uint64_t)r * n_groups + g]);
+      const float z = dgq_to_float<PT>(zeros[(uint64_t)r * n_groups + g]);
       float v[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = dgq_dequant_level((float)((w[q] >> (4 * j)) & 0xF), s, z);
-      OT* dst = out + wi * 8;
+      for (int j = 0; j < 8; ++j) {
+        const float code = __uint_as_float(0x4B000000u | ((w[q] >> (4 * j)) & 0xFu)) - 8388608.f;
+        v[j] = dgq_dequant_level(code, s, z);
+      }
+      OT* dst = out + (uint64_t)wi * 8;
       if (sizeof(OT) == 4) {
         reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
         reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
@@ -337,6 +346,8 @@ unpack_dequant_wide4_kernel(const uint32_t* __restrict__ packed, const PT* __res
         for (int j = 0; j < 8; ++j) t[j] = dgq_from_float<OT>(v[j]);
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(t);
       }
+      c += 32;
+      while (c >= words_per_row) { c -= words_per_row; ++r; }
     }
   }
 }
@@ -437,23 +448,30 @@ int32_t launch_ud_out(const void* packed, const void* scales, const void* zeros,
   const PT* s = reinterpret_cast<const PT*>(scales);
   const PT* z = reinterpret_cast<const PT*>(zeros);
   if (B == 4 && F == DGQ_FMT_BYTES_LO_FIRST && g_idx == nullptr && cols % 8 == 0 &&
-      (n_groups == 1 || group_size % 8 == 0) && dgq_aligned(packed, 4)) {
-    const int64_t n_words = (int64_t)rows * (cols / 8);
+      (n_groups == 1 || group_size % 8 == 0) && dgq_aligned(packed, 4) &&
+      (int64_t)rows * (cols / 8) < (int64_t)1 << 31) {
+    const uint32_t n_words = (uint32_t)((int64_t)rows * (cols / 8));
     const unsigned wgrid = dgq_grid(dgq_cdiv(n_words, 4), 256);
     const uint32_t* p4 = reinterpret_cast<const uint32_t*>(packed);
+    const uint32_t group_words = n_groups == 1 ? (uint32_t)(cols / 8) : (uint32_t)(group_size / 8);
+    int group_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+      if (group_words == (1u << sh)) group_shift = sh;
     switch (out_dtype) {
       case DGQ_F32:
         unpack_dequant_wide4_kernel<PT, float><<<wgrid, 256, 0, st>>>(
-            p4, s, z, reinterpret_cast<float*>(out), n_words, cols / 8, n_groups, group_size);
+            p4, s, z, reinterpret_cast<float*>(out), n_words, (uint32_t)(cols / 8), n_groups,
+            group_words, group_shift);
         return dgq_launch_status();
       case DGQ_F16:
         unpack_dequant_wide4_kernel<PT, __half><<<wgrid, 256, 0, st>>>(
-            p4, s, z, reinterpret_cast<__half*>(out), n_words, cols / 8, n_groups, group_size);
+            p4, s, z, reinterpret_cast<__half*>(out), n_words, (uint32_t)(cols / 8), n_groups,
+            group_words, group_shift);
         return dgq_launch_status();
       case DGQ_BF16:
         unpack_dequant_wide4_kernel<PT, __nv_bfloat16><<<wgrid, 256, 0, st>>>(
-            p4, s, z, reinterpret_cast<__nv_bfloat16*>(out), n_words, cols / 8, n_groups,
-            group_size);
+            p4, s, z, reinterpret_cast<__nv_bfloat16*>(out), n_words, (uint32_t)(cols / 8),
+            n_groups, group_words, group_shift);
         return dgq_launch_status();
       default:
         return DGQ_ERR_ARG;

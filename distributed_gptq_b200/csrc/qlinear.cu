@@ -3,9 +3,11 @@
 // weight byte is read exactly once, activations are staged in shared memory per
 // 512-column slice and shared by all warps of the CTA.
 //
-// qlinear_kernel (K a multiple of 8) is the main kernel; qlinear_generic_kernel covers
-// ragged K.  Both accumulate up to 16 batch rows in fp32 and dequantize with the column's
-// group scale/zero (through g_idx when given).
+// qlinear_mma_kernel is the main kernel (4-bit codes, 16-bit activations, K and the group
+// size multiples of 128); qlinear_kernel (K a multiple of 8) covers fp32 activations, byte
+// codes, small groups and g_idx on the CUDA cores; qlinear_generic_kernel covers ragged K.
+// All accumulate up to 16 batch rows in fp32 and dequantize with the column's group
+// scale/zero (through g_idx when given).
 #include "common.cuh"
 
 namespace {
@@ -285,6 +287,309 @@ qlinear_kernel(const LinArgs a, int m0) {
   }
 }
 
+// ---- tensor-core kernel -------------------------------------------------------------------------
+// 4-bit codes, fp16 or bf16 activations, K a multiple of 128, groups that are whole multiples
+// of 128 columns (or one group per row), no g_idx.  The kernel stays bound by the HBM traffic
+// of the packed weights for up to 16 batch rows because a code costs about one and a half
+// instructions: warp-level m16n8k16 multiply-accumulates take the dequantized weights
+// straight from registers (no staging in shared or tensor memory), 16 output features by
+// 8 batch rows at a time.
+//
+// A CTA owns 16 output features; its 8 warps take the 128-column steps of K round robin and
+// are summed through shared memory at the end.  In a step, lane (g, t) loads 16 bytes = 32
+// codes of feature rows g and g+8 (columns 32 t .. 32 t + 31 of the step) and the matching
+// 64 bytes of activation row g (and g+8 for more than 8 batch rows).  A byte holds two
+// adjacent columns; one byte permute (of the word and of the word shifted by 4) and one logic
+// operation turn it into a pair of 16-bit floats (magic + low nibble, magic + high nibble),
+// one packed addition per pair gives (code - zero), exactly when the zero point is an
+// integer (a second subtraction is used when it is not).  Adjacent-column pairs are exactly the fragment layout of the
+// multiply-accumulate, for the weights and for row-major activations alike.  The products
+// accumulate in fp32 per step; the group's scale is applied to the step's sums.
+template <typename T> struct MmaTraits;
+template <> struct MmaTraits<__half> {
+  static constexpr uint32_t MAGIC = 0x64006400u;   // (1024, 1024)
+  static constexpr float BASE = 1024.f;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+    const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                 "{%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+template <> struct MmaTraits<__nv_bfloat16> {
+  static constexpr uint32_t MAGIC = 0x43004300u;   // (128, 128)
+  static constexpr float BASE = 128.f;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+                 "{%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+
+// streamed once: do not keep the packed weights in L1, which holds the activations
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// eight 4-bit codes of one 32-bit word -> four pairs (code - zero) of adjacent columns
+template <typename TR, bool TWO_STEP>
+__device__ __forceinline__ void dequant_word(uint32_t w, uint32_t add2, uint32_t z2, uint32_t (&p)[4]) {
+  const uint32_t w4 = w >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // byte i of w (low nibble = even column) and of w >> 4 (low nibble = odd column)
+    const uint32_t b = __byte_perm(w, w4, ((4 + i) << 8) | i);
+    p[i] = TR::add2((b & 0x000F000Fu) | TR::MAGIC, add2);
+    if (TWO_STEP) p[i] = TR::sub2(p[i], z2);
+  }
+}
+
+constexpr int MMA_WARPS = 8;
+constexpr int MMA_STAGES = 4;   // 128-column steps of packed weights in flight per warp
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+               :: "r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+__device__ __forceinline__ void cp_async16_s(uint32_t smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t smem_src) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_src));
+  return v;
+}
+
+template <typename T, int MT>
+__global__ void __launch_bounds__(MMA_WARPS * 32)
+qlinear_mma_kernel(const LinArgs a, int m0, int n_tiles) {
+  using TR = MmaTraits<T>;
+  // per warp: a ring of steps of packed weights, filled by asynchronous copies that bypass the
+  // registers and L1; every lane reads back exactly the 2 x 16 bytes it asked for
+  __shared__ __align__(16) uint4 ring[MMA_WARPS][MMA_STAGES][2][32];
+  __shared__ float red[MMA_WARPS][16][8 * MT + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int mrows = min(8 * MT, a.M - m0);
+  const T* xbase = reinterpret_cast<const T*>(a.x) + (int64_t)m0 * a.K;
+  const T* xrow[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) xrow[mt] = xbase + (int64_t)min(g + 8 * mt, mrows - 1) * a.K + t * 32;
+  const int steps = a.K >> 7;
+  const int steps_per_group = a.n_groups == 1 ? steps : (a.group_size >> 7);
+  // The CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ..; within a tile this warp takes
+  // the contiguous steps s0 .. s0 + spw - 1.  The weight prefetch runs ahead across tiles.  The
+  // per-step bookkeeping is kept to a few additions: this kernel is bound by instruction issue.
+  const int spw = steps / MMA_WARPS + (warp < steps % MMA_WARPS ? 1 : 0);
+  const int s0 = warp * (steps / MMA_WARPS) + min(warp, steps % MMA_WARPS);
+  const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const uint32_t ring_lane = (uint32_t)__cvta_generic_to_shared(&ring[warp][0][0][lane]);
+  constexpr uint32_t SLOT_BYTES = 2 * 32 * 16, HI_BYTES = 32 * 16;
+
+  // byte offsets (below 2^32, checked by the host) of this lane's 16 bytes in rows g and g+8
+  uint32_t pf_lo = 0, pf_hi = 0;
+  int pf_tile = 0, pf_left = spw, pf_slot = 0;
+  auto pf_enter_tile = [&]() {
+    const int n_base = (blockIdx.x + pf_tile * gridDim.x) * 16;
+    const uint32_t col = (uint32_t)(s0 * 64 + t * 16);
+    pf_lo = (uint32_t)min(n_base + g, a.N_out - 1) * (uint32_t)a.row_bytes + col;
+    pf_hi = (uint32_t)min(n_base + g + 8, a.N_out - 1) * (uint32_t)a.row_bytes + col;
+  };
+  const int pf_tiles = spw > 0 ? my_tiles : 0;
+  if (pf_tiles > 0) pf_enter_tile();
+  auto prefetch = [&]() {
+    if (pf_tile < pf_tiles) {
+      cp_async16_s(ring_lane + pf_slot * SLOT_BYTES, a.qw + pf_lo);
+      cp_async16_s(ring_lane + pf_slot * SLOT_BYTES + HI_BYTES, a.qw + pf_hi);
+      pf_lo += 64; pf_hi += 64;
+      if (--pf_left == 0) {
+        pf_left = spw;
+        if (++pf_tile < pf_tiles) pf_enter_tile();
+      }
+    }
+    pf_slot = (pf_slot + 1) & (MMA_STAGES - 1);
+    cp_async_commit();          // committed even when empty: the group count stays uniform
+  };
+#pragma unroll
+  for (int i = 0; i < MMA_STAGES - 1; ++i) prefetch();
+
+  const __half2 k1024 = __float2half2_rn(1024.f), k64 = __float2half2_rn(64.f);
+  int slot = 0;
+  for (int ti = 0; ti < my_tiles; ++ti) {
+    const int n_base = (blockIdx.x + ti * gridDim.x) * 16;
+    // element offsets of the rows' group parameters, and the group of the first step
+    const int so_lo = min(n_base + g, a.N_out - 1) * a.n_groups;
+    const int so_hi = min(n_base + g + 8, a.N_out - 1) * a.n_groups;
+    float yacc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) yacc[mt][e] = 0.f;
+
+    for (int si = 0; si < spw; ++si) {
+      const int step = s0 + si;
+      prefetch();
+      // activations and group parameters of this step (L1/L2 hits) are requested before the wait
+      uint4 xv[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          xv[mt][j] = __ldg(reinterpret_cast<const uint4*>(xrow[mt] + step * 128) + j);
+      const int grp = a.n_groups == 1 ? 0 : (steps_per_group == 1 ? step : step / steps_per_group);
+      const __half hs_lo = a.scales[so_lo + grp], hs_hi = a.scales[so_hi + grp];
+      const __half hz_lo = a.zeros[so_lo + grp], hz_hi = a.zeros[so_hi + grp];
+      cp_async_wait<MMA_STAGES - 1>();
+      const uint4 cl = lds16(ring_lane + slot * SLOT_BYTES);
+      const uint4 ch = lds16(ring_lane + slot * SLOT_BYTES + HI_BYTES);
+      slot = (slot + 1) & (MMA_STAGES - 1);
+      float c[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) c[mt][e] = 0.f;
+      // Integer zero points (every GPTQ zero is one) fold into the conversion's constant.  The
+      // test runs on both rows at once in fp16: adding and removing 1024 leaves an integer alone.
+      const __half2 zz = __halves2half2(hz_lo, hz_hi);
+      const bool folded = __hbeq2(__hsub2(__hadd2(zz, k1024), k1024), zz) && __hble2(__habs2(zz), k64);
+      const float cz_lo = __half2float(hz_lo), cz_hi = __half2float(hz_hi);
+      const uint32_t wl4[4] = {cl.x, cl.y, cl.z, cl.w}, wh4[4] = {ch.x, ch.y, ch.z, ch.w};
+      if (__all_sync(0xffffffffu, folded)) {
+        const uint32_t add_lo = TR::pack(-(TR::BASE + cz_lo), -(TR::BASE + cz_lo));
+        const uint32_t add_hi = TR::pack(-(TR::BASE + cz_hi), -(TR::BASE + cz_hi));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t pl[4], ph[4];
+          dequant_word<TR, false>(wl4[j], add_lo, 0u, pl);
+          dequant_word<TR, false>(wh4[j], add_hi, 0u, ph);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            TR::mma(c[mt], pl[0], ph[0], pl[1], ph[1], xv[mt][j].x, xv[mt][j].y);
+            TR::mma(c[mt], pl[2], ph[2], pl[3], ph[3], xv[mt][j].z, xv[mt][j].w);
+          }
+        }
+      } else {
+        const uint32_t add = TR::pack(-TR::BASE, -TR::BASE);
+        const uint32_t z2_lo = TR::pack(cz_lo, cz_lo), z2_hi = TR::pack(cz_hi, cz_hi);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t pl[4], ph[4];
+          dequant_word<TR, true>(wl4[j], add, z2_lo, pl);
+          dequant_word<TR, true>(wh4[j], add, z2_hi, ph);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            TR::mma(c[mt], pl[0], ph[0], pl[1], ph[1], xv[mt][j].x, xv[mt][j].y);
+            TR::mma(c[mt], pl[2], ph[2], pl[3], ph[3], xv[mt][j].z, xv[mt][j].w);
+          }
+        }
+      }
+      const float cs_lo = __half2float(hs_lo), cs_hi = __half2float(hs_hi);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        yacc[mt][0] = fmaf(cs_lo, c[mt][0], yacc[mt][0]);
+        yacc[mt][1] = fmaf(cs_lo, c[mt][1], yacc[mt][1]);
+        yacc[mt][2] = fmaf(cs_hi, c[mt][2], yacc[mt][2]);
+        yacc[mt][3] = fmaf(cs_hi, c[mt][3], yacc[mt][3]);
+      }
+    }
+    // accumulator layout: [0], [1] = feature row g, batch rows 2t, 2t+1; [2], [3] = feature row g+8
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      red[warp][g][mt * 8 + 2 * t] = yacc[mt][0];
+      red[warp][g][mt * 8 + 2 * t + 1] = yacc[mt][1];
+      red[warp][g + 8][mt * 8 + 2 * t] = yacc[mt][2];
+      red[warp][g + 8][mt * 8 + 2 * t + 1] = yacc[mt][3];
+    }
+    __syncthreads();
+    T* y = reinterpret_cast<T*>(a.y);
+    for (int idx = threadIdx.x; idx < 16 * 8 * MT; idx += MMA_WARPS * 32) {
+      const int row = idx & 15, m = idx >> 4, n = n_base + row;
+      if (n < a.N_out && m < mrows) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < MMA_WARPS; ++w) v += red[w][row][m];
+        if (a.bias) v += load_bias<T>(a.bias, a.bias_dtype, n);
+        y[(int64_t)(m0 + m) * a.N_out + n] = dgq_from_float<T>(v);
+      }
+    }
+    __syncthreads();   // red is rewritten by the next tile
+  }
+  cp_async_wait<0>();
+}
+
+template <typename XT>
+bool launch_mma(const LinArgs& a, int m0, cudaStream_t st) { return false; }
+
+template <typename T>
+bool launch_mma_typed(const LinArgs& a, int m0, cudaStream_t st) {
+  const bool ok = a.bits == 4 && a.g_idx == nullptr && a.K % 128 == 0 && a.vec16 &&
+                  dgq_aligned(a.x, 16) && (int64_t)a.N_out * a.row_bytes < ((int64_t)1 << 32) &&
+                  (int64_t)a.N_out * a.n_groups < ((int64_t)1 << 31) &&
+                  (a.n_groups == 1 || (a.group_size > 0 && a.group_size % 128 == 0));
+  if (!ok) return false;
+  // persistent CTAs: as many as fit on the device at once, every one with the same number of
+  // 16-feature tiles (to within one)
+  const int n_tiles = (int)dgq_cdiv(a.N_out, 16);
+  const bool two = a.M - m0 > 8;
+  static int resident[2] = {0, 0};
+  if (resident[two] == 0) {
+    int per_sm = 0;
+    const cudaError_t e = two
+        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qlinear_mma_kernel<T, 2>, MMA_WARPS * 32, 0)
+        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qlinear_mma_kernel<T, 1>, MMA_WARPS * 32, 0);
+    if (e != cudaSuccess || per_sm <= 0) return false;
+    resident[two] = per_sm * dgq_sm_count();
+  }
+  const int rounds = (int)dgq_cdiv(n_tiles, resident[two]);
+  const unsigned grid = (unsigned)dgq_cdiv(n_tiles, rounds);
+  if (two) qlinear_mma_kernel<T, 2><<<grid, MMA_WARPS * 32, 0, st>>>(a, m0, n_tiles);
+  else qlinear_mma_kernel<T, 1><<<grid, MMA_WARPS * 32, 0, st>>>(a, m0, n_tiles);
+  return true;
+}
+template <>
+bool launch_mma<__half>(const LinArgs& a, int m0, cudaStream_t st) { return launch_mma_typed<__half>(a, m0, st); }
+template <>
+bool launch_mma<__nv_bfloat16>(const LinArgs& a, int m0, cudaStream_t st) {
+  return launch_mma_typed<__nv_bfloat16>(a, m0, st);
+}
+
 template <typename XT, int MC>
 void launch_fast(const LinArgs& a, int m0, cudaStream_t st) {
   constexpr int R = FastCfg<MC>::R;
@@ -313,6 +618,7 @@ template <typename XT>
 void launch_all(const LinArgs& a, cudaStream_t st) {
   for (int m0 = 0; m0 < a.M; m0 += 16) {
     int rem = a.M - m0;
+    if (launch_mma<XT>(a, m0, st)) continue;
     if (rem >= 9) launch_mc<XT, 16>(a, m0, st);
     else if (rem >= 5) launch_mc<XT, 8>(a, m0, st);
     else if (rem >= 3) launch_mc<XT, 4>(a, m0, st);

@@ -10,30 +10,47 @@ other holds one code per byte; ``n_groups = scales.shape[1]``.  ``g_idx`` is use
 as the group of every input column when its values are valid group numbers; the
 reference's constructor default ``range(in_features)`` is not, and then groups are
 runs of ``in_features // n_groups`` consecutive columns, which is what the
-reference's own dequantize-and-matmul branch computes.
+reference's own dequantize-and-matmul branch computes.  A ``g_idx`` that is exactly
+that sequential map is not passed on either, so that such layers take the kernel's
+tensor-core path.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional, Tuple
+from typing import Optional
 
 import torch
 
 from . import _C
 
 _SCHEMA = "linear(Tensor x, Tensor qweight, Tensor scales, Tensor zeros, Tensor g_idx, Tensor? bias) -> Tensor"
-_g_idx_valid: Dict[Tuple[int, int, int], bool] = {}
+_INVALID, _SEQUENTIAL, _GENERAL = 0, 1, 2
 _lib = None
 
 
+def _classify_g_idx(g_idx: torch.Tensor, n_groups: int) -> int:
+    """Looks at the values once per buffer (one device synchronisation; the answer is kept on
+    the tensor object together with its version counter): invalid group numbers, the
+    sequential map ``c // group_size`` (which the kernels compute themselves, on their fastest
+    path), or a general column-to-group map."""
+    tag = getattr(g_idx, "_dgq_g_idx_kind", None)
+    if tag is not None and tag[0] == g_idx._version and tag[1] == n_groups:
+        return tag[2]
+    K = g_idx.numel()
+    if K == 0 or int(g_idx.max()) >= n_groups or int(g_idx.min()) < 0:
+        kind = _INVALID
+    else:
+        group_size = -(-K // n_groups)
+        seq = torch.arange(K, device=g_idx.device, dtype=g_idx.dtype) // group_size
+        kind = _SEQUENTIAL if bool(torch.equal(g_idx.reshape(-1), seq)) else _GENERAL
+    try:
+        g_idx._dgq_g_idx_kind = (g_idx._version, n_groups, kind)
+    except AttributeError:
+        pass
+    return kind
+
+
 def _g_idx_usable(g_idx: torch.Tensor, n_groups: int) -> bool:
-    key = (g_idx.data_ptr(), g_idx._version, n_groups)
-    ok = _g_idx_valid.get(key)
-    if ok is None:
-        ok = bool(g_idx.numel() > 0 and int(g_idx.max()) < n_groups and int(g_idx.min()) >= 0)
-        if len(_g_idx_valid) > 4096:
-            _g_idx_valid.clear()
-        _g_idx_valid[key] = ok
-    return ok
+    return _classify_g_idx(g_idx, n_groups) != _INVALID
 
 
 def gptq_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
@@ -46,7 +63,7 @@ def gptq_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, ze
         raise RuntimeError("gptq::linear: qweight is neither nibble-packed nor one byte per code")
     n_groups = scales.shape[1]
     group_size = -(-K // n_groups)
-    gi = g_idx if _g_idx_usable(g_idx, n_groups) else None
+    gi = g_idx if _classify_g_idx(g_idx, n_groups) == _GENERAL else None
     return _C.qlinear_forward(x, qweight, scales, zeros, gi, bias, K, 4 if four_bit else 8,
                               group_size)
 

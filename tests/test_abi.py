@@ -51,3 +51,24 @@ def test_argument_validation_needs_no_device():
     assert L.dgq_pack(None, 4, 8, 4, 1, None, None) == -1
     assert L.dgq_hessian_accum(None, 16, 64, 64, None, 64, 1.0, 0, None, None) == -1
     assert L.dgq_inv_chol_upper(None, 8, 8, None, None, 0, None) == -1
+
+
+def test_g_idx_classification_is_host_logic():
+    """The operator passes a column-to-group map on to the kernels only when it is a general one:
+    the reference constructor's default (``range(in_features)``) holds no valid group numbers, and
+    the sequential map ``c // group_size`` is what the kernels compute themselves."""
+    import torch
+    from distributed_gptq_b200 import ops
+    K, g = 512, 128
+    n_groups = K // g
+    seq = (torch.arange(K) // g).to(torch.int32)
+    assert ops._classify_g_idx(seq, n_groups) == ops._SEQUENTIAL
+    assert ops._classify_g_idx(torch.arange(K, dtype=torch.int32), n_groups) == ops._INVALID
+    perm = seq[torch.randperm(K, generator=torch.Generator().manual_seed(0))].contiguous()
+    assert ops._classify_g_idx(perm, n_groups) == ops._GENERAL
+    assert ops._g_idx_usable(perm, n_groups) and ops._g_idx_usable(seq, n_groups)
+    # ragged last group: the operator can only infer ceil(K / n_groups) = 104 columns per group,
+    # so the true map (groups of 128) is a general one and is passed on
+    K2 = 520
+    seq2 = (torch.arange(K2) // 128).to(torch.int32)
+    assert ops._classify_g_idx(seq2, 5) == ops._GENERAL

@@ -34,3 +34,32 @@ def test_qlinear(dgq, M, N_out, K, g, bits, dtype):
     want2 = O.qlinear_forward(x, codes, scales, zeros, None, None, g)
     got2 = dgq.qlinear_forward(x.cuda(), qw.cuda(), scales.cuda(), zeros.cuda(), None, None, K, bits, g)
     assert float((got2.float().cpu() - want2).abs().max()) <= tol * float(want2.abs().max())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33])
+@pytest.mark.parametrize("N_out,K,g", [(64, 128, 128), (100, 512, 128), (37, 1024, 256), (256, 384, -1),
+                                       (1000, 2048, 128)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("integer_zeros", [True, False])
+def test_qlinear_tensor_core_path(dgq, M, N_out, K, g, dtype, integer_zeros):
+    """4-bit codes, 16-bit activations, whole groups of 128 columns, no g_idx: the warp-level
+    multiply-accumulate kernel.  Products are exact and accumulate in fp32, so the only rounding
+    is the output's (and, for fractional zero points, the 16-bit subtraction)."""
+    gen = torch.Generator().manual_seed(M * 11 + N_out + K)
+    codes = torch.randint(0, 16, (N_out, K), generator=gen).to(torch.uint8)
+    ng = O.n_groups(K, g)
+    scales = (torch.rand(N_out, ng, generator=gen) * 0.02 + 0.001).half()
+    if integer_zeros:
+        zeros = torch.randint(0, 16, (N_out, ng), generator=gen).half()
+    else:
+        zeros = (torch.rand(N_out, ng, generator=gen) * 15).half()
+    bias = torch.randn(N_out, generator=gen).to(dtype)
+    x = torch.randn(M, K, generator=gen).to(dtype)
+    qw = O.pack_f2(codes, 4)
+    want = O.qlinear_forward(x, codes, scales, zeros, None, bias, g)
+    got = dgq.qlinear_forward(x.cuda(), qw.cuda(), scales.cuda(), zeros.cuda(), None, bias.cuda(), K, 4, g)
+    assert got.dtype == dtype and tuple(got.shape) == (M, N_out)
+    tol = {torch.float16: 6e-4, torch.bfloat16: 4.5e-3}[dtype]
+    if not integer_zeros:
+        tol *= 2
+    assert float((got.float().cpu() - want).abs().max()) <= tol * float(want.abs().max())
