@@ -12,6 +12,14 @@ bool dgq_use_tensor_gemm() {
   return !(e && e[0] != '\0' && e[0] != '0');
 }
 
+bool dgq_use_pdl() {
+  static const bool on = [] {
+    const char* e = std::getenv("DGQ_NO_PDL");
+    return !(e && e[0] != '\0' && e[0] != '0');
+  }();
+  return on;
+}
+
 DGQ_EXPORT int64_t dgq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 DGQ_EXPORT int32_t dgq_version(void) { return 100; }

@@ -30,6 +30,39 @@ static inline int32_t dgq_launch_status(int64_t launched = 1) {
 // products of the inverse factor and of the trailing update then stay on the CUDA cores.
 bool dgq_use_tensor_gemm();
 
+// False when the environment variable DGQ_NO_PDL is set to a non-zero value: the kernels of
+// the latency-bound chains (inverse factor, block quantization) are then launched without
+// programmatic dependent launch.
+bool dgq_use_pdl();
+
+// Programmatic dependent launch for chains of short dependent kernels.  A kernel launched
+// through dgq_launch_chained may be scheduled while its predecessor in the stream is still
+// running; it does its set-up (shared memory, barriers, tensor memory), and must execute
+// dgq_chain_wait() before its first access to global memory: the wait returns when the
+// predecessor has completed and its writes are visible.  dgq_chain_release() lets the next
+// kernel of the chain be scheduled early in the same way.  Both are no-ops for a kernel that
+// was launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void dgq_chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dgq_chain_release() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dgq_launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                             size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dgq_use_pdl() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 static inline bool dgq_aligned(const void* p, uintptr_t a) {
   return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
 }

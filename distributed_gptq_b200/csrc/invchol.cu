@@ -41,6 +41,8 @@ constexpr int NB = 128;  // leaf size: blocks of at most NB x NB are handled by 
 __global__ void __launch_bounds__(256)
 reverse_in_kernel(const float* __restrict__ A, int64_t lda, float* __restrict__ V, int64_t ldv,
                   int K) {
+  dgq_chain_release();
+  dgq_chain_wait();
   const int64_t total = (int64_t)K * K;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
@@ -52,6 +54,8 @@ reverse_in_kernel(const float* __restrict__ A, int64_t lda, float* __restrict__ 
 __global__ void __launch_bounds__(256)
 reverse_out_kernel(const float* __restrict__ V, int64_t ldv, float* __restrict__ A, int64_t lda,
                    int K) {
+  dgq_chain_release();
+  dgq_chain_wait();
   const int64_t total = (int64_t)K * K;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
@@ -287,6 +291,8 @@ leaf_inv_chol_kernel(float* __restrict__ D, int64_t ldd, int nb, int32_t* info, 
   float* rdiag = T32b + HT * TL;             // [LEAF]
   float* LT = rdiag + LEAF;                  // [32][32]     transpose of the current 32 x 32 factor
   const int tid = threadIdx.x;
+  dgq_chain_release();
+  dgq_chain_wait();
   const int span = nb <= 64 ? 64 : LEAF;     // a block of at most 64 skips the 128-level
   const bool vec = nb == LEAF && (ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0;
   if (vec) {
@@ -427,8 +433,9 @@ void rec(Plan& p, int o, int n, int depth) {
   float* V = p.V;
   const int64_t ld = p.ldv;
   if (n <= NB) {
-    leaf_inv_chol_kernel<<<1, LEAF_THREADS, LEAF_SMEM_FLOATS * sizeof(float), p.st>>>(
-        V + (int64_t)o * ld + o, ld, n, p.info, p.K - 1 - o);
+    dgq_launch_chained(leaf_inv_chol_kernel, dim3(1), dim3(LEAF_THREADS),
+                       LEAF_SMEM_FLOATS * sizeof(float), p.st, V + (int64_t)o * ld + o, ld, n,
+                       p.info, p.K - 1 - o);
     ++p.leaves;
     return;
   }
@@ -505,8 +512,8 @@ DGQ_EXPORT int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t*
   p.fork = side->fork;
   p.join = side->join;
   const unsigned grid = dgq_grid((int64_t)K * K, 256);
-  reverse_in_kernel<<<grid, 256, 0, p.st>>>(A, lda, p.V, p.ldv, K);
+  dgq_launch_chained(reverse_in_kernel, dim3(grid), dim3(256), 0, p.st, A, lda, p.V, p.ldv, K);
   rec(p, 0, K, 0);
-  reverse_out_kernel<<<grid, 256, 0, p.st>>>(p.V, p.ldv, A, lda, K);
+  dgq_launch_chained(reverse_out_kernel, dim3(grid), dim3(256), 0, p.st, p.V, p.ldv, A, lda, K);
   return dgq_launch_status(2 + p.leaves);  // matrix products are counted as they are launched
 }

@@ -398,7 +398,7 @@ __device__ __forceinline__ uint4 lds16(uint32_t smem_src) {
 }
 
 template <typename T, int MT>
-__global__ void __launch_bounds__(MMA_WARPS * 32)
+__global__ void __launch_bounds__(MMA_WARPS * 32, MT == 1 ? 4 : 2)
 qlinear_mma_kernel(const LinArgs a, int m0, int n_tiles) {
   using TR = MmaTraits<T>;
   // per warp: a ring of steps of packed weights, filled by asynchronous copies that bypass the

@@ -50,11 +50,16 @@ gptq_block_kernel(const QuantArgs a) {
   extern __shared__ float Us[];  // bw x MAX_BLOCK, row j = U[i1 + j][i1 .. i1 + bw)
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  // U is an input of the entry point, complete before its first launch (a memset precedes
+  // that launch in the stream), so its block may be staged while the preceding trailing
+  // update, which only writes W, is still running; W and the error buffer wait for it.
+  dgq_chain_release();
   for (int idx = threadIdx.x; idx < a.bw * MAX_BLOCK; idx += blockDim.x) {
     int j = idx / MAX_BLOCK, c = idx % MAX_BLOCK;
     Us[idx] = (c < a.bw && c >= j) ? a.U[(int64_t)(a.i1 + j) * a.ldu + a.i1 + c] : 0.f;
   }
   __syncthreads();
+  dgq_chain_wait();
 
   double err_sq = 0.0;
   for (int row = blockIdx.x * ROWS_PER_CTA + warp; row < a.N_out; row += gridDim.x * ROWS_PER_CTA) {
@@ -211,6 +216,10 @@ gptq_block8_kernel(const QuantArgs a) {
   const int warp = threadIdx.x >> 5;
   const int sub = lane & 7;   // lane inside the row's group of eight
   const int rg = lane >> 3;   // row inside the warp
+  // U is an input of the entry point, complete before its first launch (a memset precedes
+  // that launch in the stream), so its block may be staged while the preceding trailing
+  // update, which only writes W, is still running; W and the error buffer wait for it.
+  dgq_chain_release();
   for (int idx = threadIdx.x; idx < MAX_BLOCK * MAX_BLOCK / 4; idx += blockDim.x) {
     const int j = idx / (MAX_BLOCK / 4), c4 = (idx % (MAX_BLOCK / 4)) * 4;
     const float4 u = *reinterpret_cast<const float4*>(a.U + (int64_t)(a.i1 + j) * a.ldu + a.i1 + c4);
@@ -220,6 +229,7 @@ gptq_block8_kernel(const QuantArgs a) {
     reinterpret_cast<float4*>(Us)[idx] = v;
   }
   __syncthreads();
+  dgq_chain_wait();
   const float4* Us4 = reinterpret_cast<const float4*>(Us);
   constexpr int GW = MAX_BLOCK / GPB;  // columns per group inside the block
 
@@ -427,11 +437,13 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
       if (fast_layout && gpb != 0 && a.bw == MAX_BLOCK) {
         const unsigned fgrid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, F_ROWS_PER_CTA),
                                                            (int64_t)dgq_sm_count() * 3);
-        if (gpb == 1) gptq_block8_kernel<1><<<fgrid, F_WARPS * 32, smem, st>>>(a);
-        else if (gpb == 2) gptq_block8_kernel<2><<<fgrid, F_WARPS * 32, smem, st>>>(a);
-        else gptq_block8_kernel<4><<<fgrid, F_WARPS * 32, smem, st>>>(a);
+        const dim3 fg(fgrid), fb(F_WARPS * 32);
+        if (gpb == 1) dgq_launch_chained(gptq_block8_kernel<1>, fg, fb, smem, st, a);
+        else if (gpb == 2) dgq_launch_chained(gptq_block8_kernel<2>, fg, fb, smem, st, a);
+        else dgq_launch_chained(gptq_block8_kernel<4>, fg, fb, smem, st, a);
       } else {
-        gptq_block_kernel<<<grid, ROWS_PER_CTA * 32, (size_t)a.bw * MAX_BLOCK * sizeof(float), st>>>(a);
+        dgq_launch_chained(gptq_block_kernel, dim3(grid), dim3(ROWS_PER_CTA * 32),
+                           (size_t)a.bw * MAX_BLOCK * sizeof(float), st, a);
       }
       update(a.err_off, a.bw, i1, i1 + a.bw, s1);      // rest of this super-block
     }

@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(256)
 sgemm_view_kernel(const GemmArgs g) {
   constexpr int TK = 16;
   static_assert((TM / RM) * (TN / RN) == 256, "256 threads per tile");
+  dgq_chain_release();
+  dgq_chain_wait();
   const int i0 = blockIdx.y * TM, j0 = blockIdx.x * TN;
   if (g.lower_only && j0 > i0 + TM - 1) return;
   __shared__ __align__(16) float As[2][TK][TM + 4];
@@ -150,10 +152,10 @@ inline void launch_gemm(const GemmArgs& g, cudaStream_t st) {
   if (g.m <= 0 || g.n <= 0) return;
   if (g.m > 64 && g.n > 64) {
     dim3 grid((unsigned)dgq_cdiv(g.n, 128), (unsigned)dgq_cdiv(g.m, 128));
-    sgemm_view_kernel<128, 128, 8, 8><<<grid, 256, 0, st>>>(g);
+    dgq_launch_chained(sgemm_view_kernel<128, 128, 8, 8>, grid, dim3(256), 0, st, g);
   } else {
     dim3 grid((unsigned)dgq_cdiv(g.n, 64), (unsigned)dgq_cdiv(g.m, 64));
-    sgemm_view_kernel<64, 64, 4, 4><<<grid, 256, 0, st>>>(g);
+    dgq_launch_chained(sgemm_view_kernel<64, 64, 4, 4>, grid, dim3(256), 0, st, g);
   }
   dgq_note_launches(1);
 }

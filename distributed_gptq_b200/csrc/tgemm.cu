@@ -91,6 +91,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   Control* ctl = reinterpret_cast<Control*>(epi_stage + EPI_STAGE_BYTES);
   volatile int* abort_flag = &ctl->abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  dgq_chain_release();   // the next kernel of a chain may start its own set-up
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -116,6 +117,8 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   __syncthreads();
   tc05::fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+  // set-up done; global memory is touched only after the predecessor in the stream is complete
+  dgq_chain_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -378,9 +381,10 @@ bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
   }
   p.info = g.info;
   const unsigned grid = (unsigned)std::min(p.n_tiles, dgq_sm_count());
-  tgemm_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+  const cudaError_t e = dgq_launch_chained(tgemm_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, st,
+                                           map_a, map_b, p);
   dgq_note_launches(1);
-  return cudaGetLastError() == cudaSuccess;
+  return e == cudaSuccess && cudaGetLastError() == cudaSuccess;
 }
 
 }  // namespace dgq
