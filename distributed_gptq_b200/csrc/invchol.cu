@@ -113,13 +113,14 @@ __device__ __noinline__ void chol32(const float* __restrict__ S, float* __restri
     a[4 * q] = v.x; a[4 * q + 1] = v.y; a[4 * q + 2] = v.z; a[4 * q + 3] = v.w;
   }
   float d = __shfl_sync(0xffffffffu, a[0], 0);
+  int first_bad = HT;   // first step whose pivot was not positive and finite
 #pragma unroll
   for (int k = 0; k < HT; ++k) {
-    if (!(d > 0.f) || !isfinite(d)) {
-      if (lane == k && info && atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
-        info[1] = pivot_base - k;
-      d = 1.f;
-    }
+    // no branch inside the loop: the steps stay one basic block, so that the update of step k
+    // is scheduled beside the reciprocal square root of step k+1
+    const bool bad = !(d > 0.f) || !isfinite(d);
+    first_bad = (bad && first_bad == HT) ? k : first_bad;
+    d = bad ? 1.f : d;
     const float rs = rsqrt_newton(d);
     const float l = (lane == k) ? d * rs : (lane > k ? a[k] * rs : 0.f);
     LT[k * HT + lane] = l;
@@ -137,6 +138,9 @@ __device__ __noinline__ void chol32(const float* __restrict__ S, float* __restri
       for (int j = k + 1; j < HT; ++j) a[j] = fmaf(-l, lr[j], a[j]);
     }
   }
+  if (first_bad < HT && lane == first_bad && info &&
+      atomicCAS(info, DGQ_INFO_OK, DGQ_INFO_NOT_POSDEF) == DGQ_INFO_OK)
+    info[1] = pivot_base - first_bad;
 }
 
 // X[r0.., r0..] = inverse of the lower-triangular tile whose transpose is in LT.  One warp:
