@@ -33,7 +33,11 @@ import sys
 import threading
 import time
 
-import torch
+# more hardware work queues than the default 8: the step uses a dozen streams (see
+# distributed_gptq_b200/__init__.py); must be in the environment before the CUDA context exists
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
+import torch  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -164,6 +168,11 @@ class Sweep:
         self.X_host = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # Streams are made once: torch's caching allocator keeps a pool of freed blocks per
+        # stream, so fresh streams every step would find their pools empty and call cudaMalloc.
+        from distributed_gptq_b200.streams import ChainPool
+        self.pool = ChainPool(device, n_streams=4)
+        self.copy_stream = torch.cuda.Stream(device=device)
 
     def load_device_inputs(self):
         self.X_dev = [make_activations(i, k, self.my_seqs, self.device)
@@ -182,28 +191,43 @@ class Sweep:
         for s in range(0, x.shape[0], CHUNK_SEQS):
             yield x[s:s + CHUNK_SEQS]
 
-    def _finish(self, item, from_host: bool, results: list):
-        """Layer-parallel quantization: the owner of a run quantizes and packs it."""
+    def _launch(self, item, from_host: bool, pool):
+        """Layer-parallel quantization: the owner of a run quantizes and packs it.  The chain is
+        only enqueued here, on one of the pool's side streams; `_collect` waits for it."""
         from distributed_gptq_b200 import _C
         ri, q, work = item
         if work is not None:
             work.wait()
         if self.owner[ri] != self.rank:
             q.free_hessian()
-            return
+            return None
         bits = self.runs[ri][1]
-        stats = q.quantize()
         fmt = _C.FMT_BYTES_LO_FIRST if bits == 4 else _C.FMT_INT32_LE
-        packed = q.pack_weights(format=fmt)
-        out = {"run": ri, "stats": stats, "qweight": packed["packed_weights"],
-               "scales": q.scale.to(torch.float16), "zeros": q.zero.to(torch.float16),
-               "g_idx": q.g_idx}
-        if from_host:
-            for k in ("qweight", "scales", "zeros", "g_idx"):
-                host = torch.empty(out[k].shape, dtype=out[k].dtype, pin_memory=True)
-                host.copy_(out[k], non_blocking=True)
-                self.d2h_bytes += host.numel() * host.element_size()
-                out[k] = host
+
+        def chain():
+            q.quantize_launch()
+            packed = q.pack_weights(format=fmt)
+            out = {"run": ri, "qweight": packed["packed_weights"],
+                   "scales": q.scale.to(torch.float16), "zeros": q.zero.to(torch.float16),
+                   "g_idx": q.g_idx}
+            out["d2h_bytes"] = 0
+            if from_host:
+                for k in ("qweight", "scales", "zeros", "g_idx"):
+                    host = torch.empty(out[k].shape, dtype=out[k].dtype, pin_memory=True)
+                    host.copy_(out[k], non_blocking=True)
+                    out["d2h_bytes"] += host.numel() * host.element_size()
+                    out[k] = host
+            return out
+
+        return (q, pool.submit(chain))
+
+    def _collect(self, job, results: list):
+        if job is None:
+            return
+        q, fut = job
+        out = fut.result()            # the chain is enqueued (not necessarily run)
+        out["stats"] = q.quantize_finish()
+        self.d2h_bytes += out.pop("d2h_bytes")
         results.append(out)
         q.free_hessian()
 
@@ -211,7 +235,7 @@ class Sweep:
         """One sweep.  Returns the packed results of the runs this rank owns."""
         import torch.distributed as dist
         import torch.nn as nn
-        from distributed_gptq_b200 import GPTQ, _C
+        from distributed_gptq_b200 import GPTQ
         dev = self.device
         self.h2d_bytes = self.d2h_bytes = 0
         staged = None
@@ -220,7 +244,7 @@ class Sweep:
             # queued on a side stream up front (inside the timed region) and each add_batch
             # waits only for the chunk it consumes, so copies overlap the kernels.  The four
             # runs of a layer read the same device copy.
-            copy_stream = torch.cuda.Stream(device=dev)
+            copy_stream = self.copy_stream
             staged = []
             with torch.cuda.stream(copy_stream):
                 for li in range(len(LAYERS)):
@@ -232,7 +256,11 @@ class Sweep:
                         chunks.append((buf, ev))
                         self.h2d_bytes += c.numel() * c.element_size()
                     staged.append(chunks)
-        pending, results = [], []
+        pending, jobs, results = [], [], []
+        # The chains of the runs this rank owns (damped inverse, block quantization, packing:
+        # long sequences of short dependent kernels that leave most SMs idle) are spread over
+        # four side streams and run beside each other.
+        pool = self.pool
         # ---- phase A: data-parallel Hessian accumulation, reduce to the owner
         for ri, (li, bits, act) in enumerate(self.runs):
             _, N_out, K = LAYERS[li]
@@ -253,14 +281,24 @@ class Sweep:
                 q.nsamples = NSEQ
                 work = dist.reduce(q._Hbuf, dst=self.owner[ri], async_op=True)
             pending.append((ri, q, work))
-            # One GPU: quantize right away, so that the kernels of the quantization overlap
-            # the host->device copies of the following layers.  Several GPUs: every reduce is
-            # a meeting point of all ranks, so all Hessians are accumulated and reduced first
-            # and the owners then quantize their runs side by side.
-            if self.world == 1:
-                self._finish(pending.pop(0), from_host, results)
+            # Host inputs on one GPU: the accumulation waits for PCIe most of the time, so a
+            # run's chain is enqueued at once and fills the gaps between the Hessian kernels.
+            # Device-resident inputs: the Hessian kernel occupies every SM for a millisecond at
+            # a time and would starve the chains, so they follow in phase B.  Several GPUs:
+            # every reduce is a meeting point of all ranks, so all Hessians are accumulated and
+            # reduced first.
+            if self.world == 1 and from_host:
+                jobs.append(self._launch(pending.pop(0), from_host, pool))
+        # ---- phase B: layer-parallel quantization of whatever has not been enqueued yet, the
+        # longest chains first (enqueueing a chain costs the host a few milliseconds, so the
+        # long ones should be on their way while the short ones are still being enqueued)
+        pending.sort(key=lambda it: -run_cost(LAYERS[self.runs[it[0]][0]][1],
+                                              LAYERS[self.runs[it[0]][0]][2]))
         while pending:
-            self._finish(pending.pop(0), from_host, results)
+            jobs.append(self._launch(pending.pop(0), from_host, pool))
+        while jobs:
+            self._collect(jobs.pop(0), results)
+        pool.join()
         if from_host:
             torch.cuda.current_stream().synchronize()   # the asynchronous result copies
         return results
@@ -390,15 +428,21 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, label):
         sync_all()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(steps):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        marks[0].record()
+        mallocs = []
+        for i in range(steps):
+            m0 = torch.cuda.memory_stats(device).get("num_device_alloc", 0)
             fn()
-        b.record()
+            marks[i + 1].record()
+            mallocs.append(torch.cuda.memory_stats(device).get("num_device_alloc", 0) - m0)
         sync_all()
-        ms = torch.tensor([a.elapsed_time(b)], device=device)
+        per_step = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+        print(f"[bench] rank {rank} {label}: ms per step {[round(t, 1) for t in per_step]}, "
+              f"cudaMalloc calls per step {mallocs}", file=sys.stderr, flush=True)
+        ms = torch.tensor([marks[0].elapsed_time(marks[steps])], device=device)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms) / steps
@@ -413,7 +457,7 @@ def main():
     timers = _C.KernelTimers()
     _C.set_timers(timers)
     launches0 = _C.launch_count()
-    ms_step = timed(lambda: sweep.step(False), args.steps)
+    ms_step = timed(lambda: sweep.step(False), args.steps, "device-resident")
     launches = _C.launch_count() - launches0
     _C.set_timers(None)
     clocks = sampler.stop() if rank == 0 else None
@@ -427,8 +471,9 @@ def main():
         sweep.load_host_inputs()
         sweep.X_dev = None
         torch.cuda.empty_cache()
-        sweep.step(True)
-        ms_e2e = timed(lambda: sweep.step(True), max(1, args.steps))
+        for _ in range(min(2, max(1, args.warmup))):   # allocator warm-up for the host path
+            sweep.step(True)
+        ms_e2e = timed(lambda: sweep.step(True), max(1, args.steps), "host inputs")
         bt = torch.tensor([float(sweep.h2d_bytes), float(sweep.d2h_bytes)], device=device)
         if world > 1:
             dist.all_reduce(bt)

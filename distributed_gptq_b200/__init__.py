@@ -4,6 +4,15 @@ Every computation runs in hand-written sm_100a CUDA kernels reached through the
 C ABI declared in ``include/dgq.h``; there is no CPU or eager-PyTorch fallback.
 Importing the package registers ``torch.ops.gptq.linear``.
 """
+import os as _os
+
+# The chains of independent layers run on several CUDA streams (``streams.ChainPool``, plus one
+# side stream inside every damped inverse).  With the default of 8 hardware work queues, more
+# streams than that share queues and wait for each other; the variable is read when the CUDA
+# context is created, so it is set here, before anything can have created one through this
+# package.  A value chosen by the user is left alone.
+_os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 from . import ops as _ops
 from .communication import CommunicationManager, setup_communication
 from .coordinator import (DistributedConfig, DistributedGPTQCoordinator, QuantizationMode,
@@ -14,6 +23,7 @@ from .kernels import dequantize_tensor, quantize_tensor
 from .layers import QuantizedLinear, replace_with_quantized_layers
 from .quantizer import (DistributedGPTQuantizer, GPTQQuantizer, QuantizationConfig,
                         quantize_model_simple)
+from .streams import ChainPool
 
 _ops.register()
 
@@ -22,6 +32,6 @@ __all__ = [
     "GPTQQuantizer", "quantize_model_simple", "DistributedConfig", "QuantizationMode",
     "DistributedGPTQCoordinator", "create_distributed_config", "CommunicationManager",
     "setup_communication", "QuantizedLinear", "replace_with_quantized_layers", "GPTQDequantizer",
-    "dequantize_model", "quantize_tensor", "dequantize_tensor",
+    "dequantize_model", "quantize_tensor", "dequantize_tensor", "ChainPool",
 ]
 __version__ = "0.1.0"

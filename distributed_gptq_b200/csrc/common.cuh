@@ -42,6 +42,7 @@ bool dgq_use_pdl();
 // predecessor has completed and its writes are visible.  dgq_chain_release() lets the next
 // kernel of the chain be scheduled early in the same way.  Both are no-ops for a kernel that
 // was launched the ordinary way.
+constexpr unsigned DGQ_CHAIN_EARLY_MAX_CTAS = 16;
 #ifdef __CUDACC__
 __device__ __forceinline__ void dgq_chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dgq_chain_release() { asm volatile("griddepcontrol.launch_dependents;"); }
@@ -58,7 +59,11 @@ static inline cudaError_t dgq_launch_chained(void (*kernel)(KArgs...), dim3 grid
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = dgq_use_pdl() ? 1 : 0;
+  // Only small grids are launched early: the CTAs of an early kernel sit on their SMs until its
+  // predecessor is done, which is harmless for a handful of CTAs and would shut other streams
+  // out of the machine for a grid that covers it.
+  const unsigned ctas = grid.x * grid.y * grid.z;
+  cfg.numAttrs = (dgq_use_pdl() && ctas <= DGQ_CHAIN_EARLY_MAX_CTAS) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 #endif

@@ -376,28 +376,51 @@ struct Plan {
   bool use_tensor;
 };
 
-// One side stream and one pair of events per recursion depth, per host thread and device,
-// created on first use and kept for the life of the thread.
+// One side stream and one pair of events per recursion depth for every (device, caller
+// stream) this host thread has used, created on first use and kept for the life of the
+// thread: calls on different streams must not share a side stream, or they would wait for
+// each other's products.  The table is small; when it is full an entry is taken over (stream
+// order keeps that correct, it only couples the two callers).
 struct SideResources {
+  int device = -1;
+  cudaStream_t caller = nullptr;
   cudaStream_t stream = nullptr;
   cudaEvent_t fork[32] = {}, join[32] = {};
   bool ok = false;
 };
-SideResources* side_resources() {
-  thread_local SideResources per_device[16];
+SideResources* side_resources(cudaStream_t caller) {
+  constexpr int SLOTS = 16;
+  thread_local SideResources table[SLOTS];
+  thread_local int next_victim = 0;
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
-  SideResources& r = per_device[dev];
-  if (!r.ok) {
-    if (cudaStreamCreateWithFlags(&r.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  SideResources* r = nullptr;
+  for (int i = 0; i < SLOTS && !r; ++i)
+    if (table[i].ok && table[i].device == dev && table[i].caller == caller) r = &table[i];
+  for (int i = 0; i < SLOTS && !r; ++i)
+    if (!table[i].ok) r = &table[i];
+  if (!r) {
+    // take over an entry of the same device (its stream and events stay valid there)
+    for (int n = 0; n < SLOTS && !r; ++n) {
+      SideResources& c = table[(next_victim + n) % SLOTS];
+      if (c.device == dev) { r = &c; next_victim = (next_victim + n + 1) % SLOTS; }
+    }
+    if (!r) return nullptr;
+    r->caller = caller;
+    return r;
+  }
+  if (!r->ok) {
+    if (cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     for (int d = 0; d < 32; ++d) {
-      if (cudaEventCreateWithFlags(&r.fork[d], cudaEventDisableTiming) != cudaSuccess ||
-          cudaEventCreateWithFlags(&r.join[d], cudaEventDisableTiming) != cudaSuccess)
+      if (cudaEventCreateWithFlags(&r->fork[d], cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&r->join[d], cudaEventDisableTiming) != cudaSuccess)
         return nullptr;
     }
-    r.ok = true;
+    r->device = dev;
+    r->caller = caller;
+    r->ok = true;
   }
-  return &r;
+  return r;
 }
 
 int split_point(int n) {
@@ -510,7 +533,7 @@ DGQ_EXPORT int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t*
     p.T2[d] = w;
     w += round4(need[d]);
   }
-  SideResources* side = side_resources();
+  SideResources* side = side_resources(p.st);
   DGQ_REQUIRE(side != nullptr, DGQ_ERR_LAUNCH);
   p.side = side->stream;
   p.fork = side->fork;

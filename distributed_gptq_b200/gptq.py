@@ -90,6 +90,7 @@ class GPTQ:
         self.nsamples = 0
         self.columns = self._weight_matrix().shape[1]
         self._info = None
+        self._pending = None
 
     # ------------------------------------------------------------------ helpers
     def _weight_matrix(self) -> torch.Tensor:
@@ -161,12 +162,23 @@ class GPTQ:
         ``(out, n_groups)``) and ``g_idx`` (int32 group of every input column) on the
         object.  Returns the reference's stats keys plus timings-free extras.
         """
+        self.quantize_launch()
+        return self.quantize_finish()
+
+    def quantize_launch(self) -> None:
+        """First half of :meth:`quantize`: enqueues every kernel of the quantization on the
+        current CUDA stream and returns without waiting for the device, so that a caller can
+        put the chains of independent layers on different streams (see ``streams.ChainPool``)
+        or keep accumulating other Hessians meanwhile.  :meth:`quantize_finish` must follow."""
         if self._Hbuf is None or self.nsamples == 0:
             raise RuntimeError("no calibration data: call add_batch before quantize")
-        if self._info is not None:
-            _C.raise_on_info(self._info, "hessian accumulation")
+        cur = torch.cuda.current_stream(self.device)
         Wm = self._weight_matrix()
         N_out, K = Wm.shape
+        # the inputs may have been produced on another stream than the one this chain runs on
+        self._Hbuf.record_stream(cur)
+        if Wm.is_cuda:
+            Wm.record_stream(cur)
         W = Wm.to(self.device, torch.float32).contiguous().clone()
         H = self.H
         scale = float(torch.tensor(2.0 / self.nsamples, dtype=torch.float32))
@@ -188,12 +200,46 @@ class GPTQ:
         else:
             Q = Wp
             g_idx = (torch.arange(K, device=self.device, dtype=torch.int32) // g)
-        _C.raise_on_info(info, "damped inverse")
-
+        old_weight = self.layer.weight.data
         self.codes, self.scale, self.zero, self.g_idx, self.perm = codes, scales, zeros, g_idx, perm
         self.layer.weight.data = Q.reshape(self.layer.weight.shape).to(
             device=self.layer.weight.device, dtype=self.layer.weight.dtype)
-        total_error = float(terr.item())
+        # the status words and the error sum travel to pinned host memory on this stream, so that
+        # quantize_finish only has to wait for this chain, not for the stream it is called on
+        def to_host(t):
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            h.copy_(t, non_blocking=True)
+            return h
+        status = {"info": to_host(info), "terr": to_host(terr),
+                  "hessian_info": to_host(self._info) if self._info is not None else None}
+        done = torch.cuda.Event()
+        done.record(cur)
+        self._pending = {"status": status, "old_weight": old_weight, "done": done}
+
+    def quantize_finish(self) -> Dict[str, Any]:
+        """Second half of :meth:`quantize`: waits for the chain, raises if the Hessian
+        accumulation or the damped inverse reported a failure (the layer's weight is then put
+        back as it was) and returns the stats."""
+        pend = getattr(self, "_pending", None)
+        if pend is None:
+            raise RuntimeError("call quantize_launch before quantize_finish")
+        self._pending = None
+        pend["done"].synchronize()
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(pend["done"])
+        for t in (self.codes, self.scale, self.zero, self.g_idx, self.layer.weight.data):
+            if t is not None and t.is_cuda:
+                t.record_stream(cur)
+        status = pend["status"]
+        try:
+            if status["hessian_info"] is not None:
+                _C.raise_on_info(status["hessian_info"], "hessian accumulation")
+            _C.raise_on_info(status["info"], "damped inverse")
+        except Exception:
+            self.layer.weight.data = pend["old_weight"]
+            self.codes = self.scale = self.zero = self.g_idx = self.perm = None
+            raise
+        total_error = float(status["terr"].item())
         return {
             "bits": self.bits,
             "group_size": self.group_size,

@@ -23,6 +23,7 @@ from . import _C, io
 from .coordinator import (DistributedConfig, DistributedGPTQCoordinator, assign_owners,
                           create_distributed_config, layer_cost)
 from .gptq import GPTQ
+from .streams import ChainPool
 
 logger = logging.getLogger(__name__)
 
@@ -109,6 +110,7 @@ class DistributedGPTQuantizer:
         # diagnostics: when set before quantize_model, the reduced raw Hessian of every layer
         # this rank quantizes is kept (on the host) in `hessians`
         self.keep_hessians = False
+        self._pool: Optional[ChainPool] = None
         self.hessians: Dict[str, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ discovery
@@ -238,6 +240,13 @@ class DistributedGPTQuantizer:
             t0 = time.time()
             all_reduce_mode = self.dist_config.hessian_exchange != "owner" or world == 1
             results: Dict[str, dict] = {}
+            # The layers of a stage are independent once their Hessians are complete: their
+            # chains (damped inverse, block quantization, packing) are enqueued on side
+            # streams, where they run beside each other, and collected afterwards.
+            if self._pool is None:      # made once: the caching allocator pools memory per stream
+                self._pool = ChainPool(co.device, n_streams=4)
+            pool = self._pool
+            launched = []
             for g in leaders:
                 mine = all_reduce_mode or owner_of_group[g] == self.dist_config.rank
                 if mine:
@@ -247,12 +256,23 @@ class DistributedGPTQuantizer:
                             q._Hbuf, q.nsamples = quantizers[g]._Hbuf, n_global
                         if self.keep_hessians:
                             self.hessians[n] = q.H.detach().cpu().clone()
-                        stats = q.quantize()
-                        fmt = io.file_format(cfg.bits)
-                        results[n] = {"stats": stats, "packed": io.packed_state(n, q, fmt)}
-                        q.codes = None
-                        if n != g:
-                            q._Hbuf = None
+
+                        def chain(n=n, q=q):
+                            q.quantize_launch()
+                            return io.packed_state(n, q, io.file_format(cfg.bits))
+
+                        launched.append((n, g, q, pool.submit(chain)))
+            for n, g, q, fut in launched:
+                packed = fut.result()
+                stats = q.quantize_finish()
+                for t in packed.values():
+                    t.record_stream(torch.cuda.current_stream(co.device))
+                results[n] = {"stats": stats, "packed": packed}
+                q.codes = None
+                if n != g:
+                    q._Hbuf = None
+            pool.join()
+            for g in leaders:
                 quantizers[g].free_hessian()
             torch.cuda.synchronize(co.device)
             self.timings["quantize_s"] = time.time() - t0
