@@ -11,7 +11,10 @@ Workload ("layer sweep"): three bf16 linear layers (N_out x K) 4096x4096, 11008x
 activations ~N(0,1) with 1 % of the channels scaled by 20; each layer is quantized four
 times (4-bit and 3-bit, group 128, act-order off and on, blocksize 128, percdamp 0.01).
 One step = the 12 independent GPTQ runs, each: Hessian accumulation over all tokens ->
-damped inverse factor -> blockwise quantization -> packing.  All inputs are synthetic and
+damped inverse factor -> blockwise quantization -> packing.  The Hessians of all runs are
+accumulated first; the 12 chains inverse -> quantization -> packing then run on four side
+streams beside each other (with host inputs on one GPU a chain starts as soon as its
+Hessian is complete and fills the time the accumulation waits for PCIe).  All inputs are synthetic and
 seeded.  Activations (2.1 - 5.8 GB per layer) are far larger than L2, so no flush is needed
 between iterations.
 
@@ -33,11 +36,7 @@ import sys
 import threading
 import time
 
-# more hardware work queues than the default 8: the step uses a dozen streams (see
-# distributed_gptq_b200/__init__.py); must be in the environment before the CUDA context exists
-os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
-
-import torch  # noqa: E402
+import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -283,8 +282,9 @@ class Sweep:
             pending.append((ri, q, work))
             # Host inputs on one GPU: the accumulation waits for PCIe most of the time, so a
             # run's chain is enqueued at once and fills the gaps between the Hessian kernels.
-            # Device-resident inputs: the Hessian kernel occupies every SM for a millisecond at
-            # a time and would starve the chains, so they follow in phase B.  Several GPUs:
+            # Device-resident inputs: the Hessian kernels saturate the GPU (tensor pipe and power
+            # cap), chains enqueued beside them only slowed both down in measurements, so they
+            # follow in phase B.  Several GPUs:
             # every reduce is a meeting point of all ranks, so all Hessians are accumulated and
             # reduced first.
             if self.world == 1 and from_host:

@@ -4,15 +4,6 @@ Every computation runs in hand-written sm_100a CUDA kernels reached through the
 C ABI declared in ``include/dgq.h``; there is no CPU or eager-PyTorch fallback.
 Importing the package registers ``torch.ops.gptq.linear``.
 """
-import os as _os
-
-# The chains of independent layers run on several CUDA streams (``streams.ChainPool``, plus one
-# side stream inside every damped inverse).  With the default of 8 hardware work queues, more
-# streams than that share queues and wait for each other; the variable is read when the CUDA
-# context is created, so it is set here, before anything can have created one through this
-# package.  A value chosen by the user is left alone.
-_os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
-
 from . import ops as _ops
 from .communication import CommunicationManager, setup_communication
 from .coordinator import (DistributedConfig, DistributedGPTQCoordinator, QuantizationMode,

@@ -332,7 +332,11 @@ DGQ_EXPORT int32_t dgq_hessian_accum(const void* X, int64_t T, int32_t K, int64_
   p.n_work = p.n_tiles * s;
   p.info = info;
 
-  unsigned grid = (unsigned)std::min<int64_t>(p.n_work, sms);
+  // Work items are dealt round robin, so the kernel lasts as long as the CTA with the most
+  // items: the smallest grid with that many rounds is as fast as one CTA per SM and leaves
+  // the other SMs to kernels on other streams (K = 11008: 946 items, 7 rounds, 136 CTAs).
+  const int64_t rounds = dgq_cdiv(p.n_work, sms);
+  unsigned grid = (unsigned)dgq_cdiv(p.n_work, rounds);
   hessian_syrk_kernel<<<grid, THREADS, SMEM_BYTES, dgq_stream(stream)>>>(tmap, p);
   return dgq_launch_status();
 }
