@@ -37,6 +37,8 @@ class ChainPool:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("ChainPool needs a CUDA device")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         n = max(1, n_streams)
         self.streams = [torch.cuda.Stream(device=self.device, priority=-1) for _ in range(n)]
         self._workers = ([ThreadPoolExecutor(max_workers=1, thread_name_prefix=f"dgq-chain{i}")

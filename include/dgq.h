@@ -119,6 +119,10 @@ int32_t dgq_permute_cols_u8(const uint8_t* src, int64_t lds, uint8_t* dst, int64
  * (fp32-accurate tensor-core products above 128 x 128, one CTA per 128 x 128 leaf).
  * info (device, 2 x int32): DGQ_INFO_NOT_POSDEF and the pivot index on failure.
  * lda a multiple of 4, A 16-byte aligned.
+ * Part of the work runs on a side stream that the library creates on first use for
+ * every (host thread, device, caller stream) and joins back into `stream` before the
+ * call's last kernels, so the call is ordered on `stream` like any other.  Make the
+ * first call for a stream outside a stream capture (streams and events are created).
  */
 int64_t dgq_inv_chol_workspace_bytes(int32_t K);
 int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t* info,
