@@ -1,0 +1,96 @@
+"""The layer-sweep sizes (K = 4096 and 11008), checked through properties that do not need the
+CPU oracle: the factor identity of the damped inverse, the quantizer's invariants and its gain
+over round-to-nearest, the pack round trip, and the quantized linear against a dequantized
+matmul.  torch on the device is the checker here, never the thing under test."""
+import pytest
+import torch
+import torch.nn as nn
+
+pytestmark = pytest.mark.gpu
+
+
+def _hessian(K, T, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(T, K, generator=g, device="cuda")
+    x[:, ::97] *= 20.0
+    return x
+
+
+@pytest.mark.parametrize("K", [4096, 11008])
+def test_inverse_factor_identity(dgq, K):
+    x = _hessian(K, 2 * K, K)
+    H = (x.t() @ x) * (2.0 / x.shape[0])
+    H += torch.eye(K, device="cuda") * (0.01 * float(H.diagonal().mean()))
+    A = H.clone()
+    info = dgq.new_info("cuda")
+    U = dgq.inv_chol_upper(A, info)
+    assert info.tolist() == [0, 0]
+    assert float(U.tril(-1).abs().max()) == 0.0 and float(U.diagonal().min()) > 0.0
+    # U^T U H = I, evaluated in fp64 on a block of columns to keep the checker cheap
+    cols = slice(0, 512)
+    R = (U.double().t() @ (U.double() @ H.double()[:, cols]))
+    R[cols, :] -= torch.eye(512, dtype=torch.float64, device="cuda")
+    assert float(R.abs().max()) <= 2e-4
+    # and against torch's own chain on the same matrix
+    L = torch.linalg.cholesky(H.double())
+    want = torch.linalg.cholesky(torch.cholesky_inverse(L), upper=True)
+    assert float((U.double() - want).abs().max()) <= 1e-4 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("N_out,K,bits,act", [(4096, 4096, 4, False), (4096, 11008, 3, True)])
+def test_quantizer_invariants_at_sweep_size(dgq, N_out, K, bits, act):
+    from distributed_gptq_b200 import GPTQ
+    g = torch.Generator(device="cuda").manual_seed(N_out + K)
+    lin = nn.Linear(K, N_out, bias=False, device="cuda", dtype=torch.bfloat16)
+    lin.weight.data = (torch.randn(N_out, K, generator=g, device="cuda") * 0.02).bfloat16()
+    W0 = lin.weight.data.float().clone()
+    x = _hessian(K, 16384, 7).bfloat16()
+    q = GPTQ(lin, bits=bits, group_size=128, actorder=act, device="cuda")
+    q.add_batch(x.reshape(8, -1, K), None)
+    H = q.H.clone() * (2.0 / q.nsamples)
+    stats = q.quantize()
+    maxq = 2 ** bits - 1
+    assert int(q.codes.max()) <= maxq and q.codes.dtype == torch.uint8
+    # the weight written back is exactly the dequantized codes (in the layer's dtype)
+    gi = q.g_idx.long()
+    deq = (q.codes.float() - q.zero[:, gi]) * q.scale[:, gi]
+    assert torch.equal(deq.bfloat16(), lin.weight.data)
+    # g_idx is the permuted sequential map, zero points are integers in range
+    assert torch.equal(torch.sort(gi).values, torch.arange(K, device="cuda") // 128)
+    assert torch.equal(q.zero, q.zero.round()) and float(q.zero.min()) >= 0 and float(q.zero.max()) <= maxq
+    # error feedback pays: tr((W-Q) H (W-Q)^T) is below round-to-nearest with the same grid size
+    def hess_err(Q):
+        D = (W0 - Q)
+        return float(((D @ H) * D).sum())
+    Wg = W0.view(N_out, K // 128, 128)
+    mn, mx = Wg.amin(-1, keepdim=True).clamp(max=0), Wg.amax(-1, keepdim=True).clamp(min=0)
+    sc = (mx - mn) / maxq
+    sc = torch.where(sc == 0, torch.ones_like(sc), sc)
+    zp = torch.round(-mn / sc)
+    rtn = ((torch.clamp(torch.round(Wg / sc + zp), 0, maxq) - zp) * sc).view(N_out, K)
+    e_gptq, e_rtn = hess_err(deq), hess_err(rtn)
+    assert e_gptq < 0.95 * e_rtn       # nearly uncorrelated inputs: the gain is modest (0.88 measured)
+    assert stats["total_error"] > 0
+    # pack -> unpack is the identity in every format
+    for fmt in (dgq.FMT_BYTES_HI_FIRST, dgq.FMT_BYTES_LO_FIRST, dgq.FMT_INT32_LE):
+        if fmt == dgq.FMT_BYTES_HI_FIRST and bits == 3:
+            continue
+        assert torch.equal(dgq.unpack(dgq.pack(q.codes, bits, fmt), K, bits, fmt), q.codes)
+
+
+@pytest.mark.parametrize("M", [1, 16])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_quantized_linear_at_sweep_size(dgq, M, dtype):
+    N_out, K, g = 13824, 5120, 128
+    gen = torch.Generator(device="cuda").manual_seed(M)
+    codes = torch.randint(0, 16, (N_out, K), generator=gen, device="cuda", dtype=torch.uint8)
+    scales = (torch.rand(N_out, K // g, generator=gen, device="cuda") * 0.02 + 0.001).half()
+    zeros = torch.randint(0, 16, (N_out, K // g), generator=gen, device="cuda").half()
+    x = torch.randn(M, K, generator=gen, device="cuda").to(dtype)
+    qw = dgq.pack(codes, 4, dgq.FMT_BYTES_LO_FIRST)
+    got = dgq.qlinear_forward(x, qw, scales, zeros, None, None, K, 4, g)
+    gi = torch.arange(K, device="cuda") // g
+    W = (codes.float() - zeros.float()[:, gi]) * scales.float()[:, gi]
+    want = x.double() @ W.double().t()
+    tol = {torch.float16: 6e-4, torch.bfloat16: 4.5e-3}[dtype]
+    assert float((got.double() - want).abs().max()) <= tol * float(want.abs().max())
