@@ -12,7 +12,7 @@ activations ~N(0,1) with 1 % of the channels scaled by 20; each layer is quantiz
 times (4-bit and 3-bit, group 128, act-order off and on, blocksize 128, percdamp 0.01).
 One step = the 12 independent GPTQ runs, each: Hessian accumulation over all tokens ->
 damped inverse factor -> blockwise quantization -> packing.  The Hessians of all runs are
-accumulated first; the 12 chains inverse -> quantization -> packing then run on four side
+accumulated first; the 12 chains inverse -> quantization -> packing then run on six side
 streams beside each other (with host inputs on one GPU a chain starts as soon as its
 Hessian is complete and fills the time the accumulation waits for PCIe).  All inputs are synthetic and
 seeded.  Activations (2.1 - 5.8 GB per layer) are far larger than L2, so no flush is needed
@@ -170,7 +170,7 @@ class Sweep:
         # Streams are made once: torch's caching allocator keeps a pool of freed blocks per
         # stream, so fresh streams every step would find their pools empty and call cudaMalloc.
         from distributed_gptq_b200.streams import ChainPool
-        self.pool = ChainPool(device, n_streams=4)
+        self.pool = ChainPool(device, n_streams=6)
         self.copy_stream = torch.cuda.Stream(device=device)
 
     def load_device_inputs(self):
@@ -258,7 +258,8 @@ class Sweep:
         pending, jobs, results = [], [], []
         # The chains of the runs this rank owns (damped inverse, block quantization, packing:
         # long sequences of short dependent kernels that leave most SMs idle) are spread over
-        # four side streams and run beside each other.
+        # six side streams and run beside each other (2 / 4 / 6 / 12 streams: 240 / 225 / 220 /
+        # 220 ms per step; enqueueing all chains costs the host 18-30 ms, hidden under phase A).
         pool = self.pool
         # ---- phase A: data-parallel Hessian accumulation, reduce to the owner
         for ri, (li, bits, act) in enumerate(self.runs):
