@@ -4,9 +4,15 @@
 // B (128 x 32, or 32 x 128 as four 32 x 32 panels) into 128-byte-swizzled shared memory
 // (32-byte swizzle atoms for the n-contiguous form of B, as tf32 operands require);
 // four converter warps split every element x into hi = tf32(x) (round to nearest) and
-// lo = x - hi, writing hi in place and lo into a twin buffer at the same (swizzled)
-// offset; one thread then issues, per 8 reduction steps, three tcgen05.mma kind::tf32
-// instructions (hi*hi, hi*lo, lo*hi) into a 128 x 128 fp32 accumulator in tensor memory.
+// lo = x - hi.  For B, hi is written in place and lo into a twin buffer at the same
+// (swizzled) offset.  For A, converter thread r owns row r of the tile and writes hi and lo
+// into tensor memory (32 columns each per stage), from where the products read their A
+// operand: the kernel is bound by shared-memory bandwidth (TMA writes, converter traffic and
+// the operand reads of three products per slice), and this takes A's converter writes and
+// all A operand reads off it (224 -> 144 KB of shared-memory traffic per slice; 4096^3:
+// 165 -> 205 TFLOP/s fp32-equivalent).  One thread then issues, per 8 reduction steps, three
+// tcgen05.mma kind::tf32 instructions (lo*hi, hi*lo, hi*hi) into a 128 x 128 fp32
+// accumulator in tensor memory.
 // Accumulators are double buffered so that the epilogue warps (TMEM -> registers -> a
 // warp-private swizzled staging tile in shared memory -> alpha/beta update with whole
 // 128-byte lines of C per row) overlap the next tile's main loop.  CTAs are persistent
@@ -16,6 +22,7 @@
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, reports
 // DGQ_INFO_WAIT_TIMEOUT, waits for copies in flight, frees its tensor memory and returns.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "tc05.cuh"
@@ -30,6 +37,8 @@ constexpr int STAGE_BYTES = 4 * OPERAND_BYTES;     // A hi, A lo, B hi, B lo
 constexpr int STAGES = 3;
 constexpr int THREADS = 320;
 constexpr uint32_t TMEM_COLS = 256;                // two 128-column accumulators
+constexpr uint32_t TMEM_COLS_TS = 512;             // + per stage 32 columns of A hi and 32 of A lo
+constexpr uint32_t TS_A_COL0 = 256, TS_A_STAGE_COLS = 64;
 constexpr int EPI_STAGE_BYTES = 4 * 32 * 128;        // per epilogue warp: 32 rows x 32 fp32 columns
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256;
 
@@ -81,6 +90,7 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(r);
 }
 
+template <bool TS /* A operand of the products from tensor memory */>
 __global__ void __launch_bounds__(THREADS, 1)
 tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const Params p) {
@@ -110,7 +120,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   }
   if (warp == 0) {
     __syncwarp();
-    tc05::tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tc05::tmem_alloc(&ctl->tmem_base, TS ? TMEM_COLS_TS : TMEM_COLS);
     tc05::tmem_relinquish();
   }
   tc05::fence_before_sync();
@@ -194,9 +204,17 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             const uint64_t da_lo = tc05::make_smem_desc(a_lo + a_off, 0, 1024);
             const uint64_t db_hi = tc05::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_layout);
             const uint64_t db_lo = tc05::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_layout);
-            tc05::umma_tf32(acc, da_lo, db_hi, idesc, (s_ | k8) != 0 ? 1u : 0u);
-            tc05::umma_tf32(acc, da_hi, db_lo, idesc, 1u);
-            tc05::umma_tf32(acc, da_hi, db_hi, idesc, 1u);
+            if (TS) {
+              const uint32_t ta_hi = tmem_base + TS_A_COL0 + s * TS_A_STAGE_COLS + k8 * 8;
+              const uint32_t ta_lo = ta_hi + 32;
+              tc05::umma_tf32_ts(acc, ta_lo, db_hi, idesc, (s_ | k8) != 0 ? 1u : 0u);
+              tc05::umma_tf32_ts(acc, ta_hi, db_lo, idesc, 1u);
+              tc05::umma_tf32_ts(acc, ta_hi, db_hi, idesc, 1u);
+            } else {
+              tc05::umma_tf32(acc, da_lo, db_hi, idesc, (s_ | k8) != 0 ? 1u : 0u);
+              tc05::umma_tf32(acc, da_hi, db_lo, idesc, 1u);
+              tc05::umma_tf32(acc, da_hi, db_hi, idesc, 1u);
+            }
           }
           tc05::umma_commit(&ctl->empty[s]);
         }
@@ -223,6 +241,39 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         float4* lo_a = hi_a + OPERAND_BYTES / 16;
         float4* hi_b = hi_a + 2 * (OPERAND_BYTES / 16);
         float4* lo_b = hi_a + 3 * (OPERAND_BYTES / 16);
+        if (TS) {
+          // B is split in shared memory as below; A goes to tensor memory: this thread owns row
+          // (32 * (warp % 4) + lane) of the tile, reads its 128 bytes (eight 16-byte pieces,
+          // XOR-swizzled by the row) and writes 32 columns of hi and 32 of lo.
+#pragma unroll
+          for (int r = 0; r < OPERAND_BYTES / 16 / 128; ++r) {
+            const int idx = ct + r * 128;
+            const float4 xb = hi_b[idx];
+            float4 hb, lb;
+            hb.x = to_tf32(xb.x); hb.y = to_tf32(xb.y); hb.z = to_tf32(xb.z); hb.w = to_tf32(xb.w);
+            lb.x = xb.x - hb.x; lb.y = xb.y - hb.y; lb.z = xb.z - hb.z; lb.w = xb.w - hb.w;
+            hi_b[idx] = hb; lo_b[idx] = lb;
+          }
+          const int row = (warp & 3) * 32 + lane;
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 v = hi_a[row * 8 + (c ^ (row & 7))];
+            const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float h = to_tf32(x[e]);
+              hi[4 * c + e] = __float_as_uint(h);
+              lo[4 * c + e] = __float_as_uint(x[e] - h);
+            }
+          }
+          const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + TS_A_COL0 +
+                              s * TS_A_STAGE_COLS;
+          tc05::tmem_st_32x32(ta, hi);
+          tc05::tmem_st_32x32(ta + 32, lo);
+          tc05::tmem_st_wait();
+          tc05::fence_before_sync();
+        } else {
 #pragma unroll
         for (int r = 0; r < OPERAND_BYTES / 16 / 128; ++r) {
           const int idx = ct + r * 128;
@@ -233,6 +284,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           hb.x = to_tf32(xb.x); hb.y = to_tf32(xb.y); hb.z = to_tf32(xb.z); hb.w = to_tf32(xb.w);
           lb.x = xb.x - hb.x; lb.y = xb.y - hb.y; lb.z = xb.z - hb.z; lb.w = xb.w - hb.w;
           hi_a[idx] = ha; lo_a[idx] = la; hi_b[idx] = hb; lo_b[idx] = lb;
+        }
         }
         // make the generic-proxy writes visible to the tensor core's (async proxy) reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -330,7 +382,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   }
   if (warp == 0) {
     tc05::fence_after_sync();
-    tc05::tmem_dealloc(tmem_base, TMEM_COLS);
+    tc05::tmem_dealloc(tmem_base, TS ? TMEM_COLS_TS : TMEM_COLS);
   }
 }
 
@@ -349,7 +401,9 @@ bool tgemm_supported(const TGemmArgs& g) {
 bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(tgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(tgemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(tgemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)SMEM_BYTES) != cudaSuccess)
       return false;
     attr_set = true;
@@ -381,8 +435,15 @@ bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
   }
   p.info = g.info;
   const unsigned grid = (unsigned)std::min(p.n_tiles, dgq_sm_count());
-  const cudaError_t e = dgq_launch_chained(tgemm_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, st,
-                                           map_a, map_b, p);
+  // A operand from tensor memory unless DGQ_TGEMM_SS is set to a non-zero value (then both
+  // operands of every product come from shared memory)
+  static const bool a_from_tmem = [] {
+    const char* v = std::getenv("DGQ_TGEMM_SS");
+    return !(v && v[0] != '\0' && v[0] != '0');
+  }();
+  const cudaError_t e = a_from_tmem
+      ? dgq_launch_chained(tgemm_kernel<true>, dim3(grid), dim3(THREADS), SMEM_BYTES, st, map_a, map_b, p)
+      : dgq_launch_chained(tgemm_kernel<false>, dim3(grid), dim3(THREADS), SMEM_BYTES, st, map_a, map_b, p);
   dgq_note_launches(1);
   return e == cudaSuccess && cudaGetLastError() == cudaSuccess;
 }
