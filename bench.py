@@ -45,7 +45,7 @@ LAYERS = [("4096x4096", 4096, 4096), ("11008x4096", 11008, 4096), ("4096x11008",
 SETTINGS = [(4, False), (4, True), (3, False), (3, True)]   # (bits, act-order)
 NSEQ, SEQ = 128, 2048
 GROUP, BLOCK, PERCDAMP = 128, 128, 0.01
-CHUNK_SEQS = 16          # sequences per add_batch call
+CHUNK_SEQS = 32          # sequences per add_batch call
 HESS_TILE = 256
 
 
