@@ -32,6 +32,8 @@ SIGNATURES = {
     "dgq_device_check": (_I32, []),
     "dgq_launch_count": (_I64, []),
     "dgq_hessian_accum": (_I32, [_P, _I64, _I32, _I64, _P, _I64, _F, _I32, _P, _P]),
+    "dgq_hessian_accum_upper": (_I32, [_P, _I64, _I32, _I64, _P, _I64, _F, _I32, _P, _P]),
+    "dgq_hessian_mirror": (_I32, [_P, _I32, _I64, _P]),
     "dgq_cast_f32_to_bf16": (_I32, [_P, _P, _I64, _P]),
     "dgq_cast_f16_to_bf16": (_I32, [_P, _P, _I64, _P]),
     "dgq_actorder_perm": (_I32, [_P, _I32, _I64, _F, _P, _P, _P]),
@@ -45,6 +47,8 @@ SIGNATURES = {
     "dgq_gptq_quantize_workspace_bytes": (_I64, [_I32, _I32, _I32]),
     "dgq_gptq_quantize": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _P, _I64,
                                  _P, _P, _P, _P, _I64, _P]),
+    "dgq_gptq_quantize_rows": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _P, _I64,
+                                      _P, _P, _P, _P, _P, _I64, _P]),
     "dgq_gptq_quantize_noalloc_max_rows": (_I32, []),
     "dgq_gptq_quantize_noalloc": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _I32, _I32, _I32, _P, _I64,
                                          _P, _P, _P, _P]),
@@ -193,16 +197,28 @@ def to_bf16(x: torch.Tensor) -> torch.Tensor:
 
 
 def hessian_accum(X: torch.Tensor, H: torch.Tensor, alpha: float = 1.0, splits: int = 0,
-                  info: Optional[torch.Tensor] = None) -> None:
-    """``H += alpha * XᵀX`` with X ``(T, K)`` bf16 and H ``(K, K)`` fp32, in place."""
+                  info: Optional[torch.Tensor] = None, upper_only: bool = False) -> None:
+    """``H += alpha * XᵀX`` with X ``(T, K)`` bf16 and H ``(K, K)`` fp32, in place.  With
+    ``upper_only`` only the part on and above the diagonal is updated (see
+    :func:`hessian_mirror`)."""
     _require_cuda(X, H)
     assert X.dim() == 2 and X.dtype == torch.bfloat16 and X.stride(1) == 1
     assert H.dtype == torch.float32 and H.dim() == 2 and H.stride(1) == 1
     T, K = X.shape
     assert H.shape == (K, K)
+    fn = lib().dgq_hessian_accum_upper if upper_only else lib().dgq_hessian_accum
     with torch.cuda.device(X.device), _timed("hessian_accum"):
-        check(lib().dgq_hessian_accum(_ptr(X), T, K, X.stride(0), _ptr(H), H.stride(0), alpha,
-                                      splits, _ptr(info), _stream()), "dgq_hessian_accum")
+        check(fn(_ptr(X), T, K, X.stride(0), _ptr(H), H.stride(0), alpha, splits, _ptr(info),
+                 _stream()), "dgq_hessian_accum")
+
+
+def hessian_mirror(H: torch.Tensor) -> None:
+    """Copies the part of H above the diagonal to below it, in place."""
+    _require_cuda(H)
+    assert H.dtype == torch.float32 and H.dim() == 2 and H.stride(1) == 1
+    with torch.cuda.device(H.device), _timed("prepare"):
+        check(lib().dgq_hessian_mirror(_ptr(H), H.shape[0], H.stride(0), _stream()),
+              "dgq_hessian_mirror")
 
 
 # --------------------------------------------------------------------------- preparation
@@ -280,10 +296,13 @@ def gemm_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, b_is_kn: bool, a
     return c
 
 
-def gptq_quantize(W: torch.Tensor, U: torch.Tensor, bits: int, group_size: int, blocksize: int):
+def gptq_quantize(W: torch.Tensor, U: torch.Tensor, bits: int, group_size: int, blocksize: int,
+                  row_error: bool = False, ws_bytes: Optional[int] = None):
     """Quantizes W ``(N_out, K)`` fp32 in place (it becomes the dequantized Q).
 
-    Returns ``(codes uint8, scales fp32, zeros fp32, total_error device double)``."""
+    Returns ``(codes uint8, scales fp32, zeros fp32, total_error device double)``; with
+    ``row_error=True`` the last element is the ``(N_out,)`` device vector of per-row error
+    sums instead.  ``ws_bytes`` overrides the workspace size (tests of small workspaces)."""
     _require_cuda(W, U)
     assert W.dtype == torch.float32 and W.stride(1) == 1 and U.dtype == torch.float32
     N_out, K = W.shape
@@ -295,13 +314,17 @@ def gptq_quantize(W: torch.Tensor, U: torch.Tensor, bits: int, group_size: int, 
     terr = torch.zeros(1, dtype=torch.float64, device=W.device)
     nbytes = lib().dgq_gptq_quantize_workspace_bytes(N_out, K, blocksize)
     check(min(nbytes, 0), "dgq_gptq_quantize_workspace_bytes")
+    if ws_bytes is not None:
+        nbytes = int(ws_bytes)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
+    rerr = torch.empty(N_out, dtype=torch.float64, device=W.device) if row_error else None
     with torch.cuda.device(W.device), _timed("gptq_quantize"):
-        check(lib().dgq_gptq_quantize(_ptr(W), W.stride(0), _ptr(U), U.stride(0), N_out, K, bits,
-                                      group_size, blocksize, _ptr(codes), K, _ptr(scales),
-                                      _ptr(zeros), _ptr(terr), _ptr(ws), nbytes, _stream()),
+        check(lib().dgq_gptq_quantize_rows(_ptr(W), W.stride(0), _ptr(U), U.stride(0), N_out, K,
+                                           bits, group_size, blocksize, _ptr(codes), K,
+                                           _ptr(scales), _ptr(zeros), _ptr(terr), _ptr(rerr),
+                                           _ptr(ws), nbytes, _stream()),
               "dgq_gptq_quantize")
-    return codes, scales, zeros, terr
+    return codes, scales, zeros, (rerr if row_error else terr)
 
 
 def find_params(x: torch.Tensor, bits: int):

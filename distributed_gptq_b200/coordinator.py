@@ -152,6 +152,58 @@ class DistributedGPTQCoordinator:
         idx = shard_indices(len(samples), self.config.rank, self.config.world_size)
         return [samples[i] for i in idx]
 
+    def distribute_calibration_data(self, dataloader):
+        """This rank's share of the calibration data (reference ``coordinator.py:147-181``).
+        A ``DataLoader`` comes back as a ``DataLoader`` over the same dataset restricted to
+        items r, r+W, ... (the reference's ``DistributedSampler(shuffle=False)`` split, without
+        the duplicates it pads with); any other sequence comes back as the list of its items
+        r, r+W, ....  A single process gets its argument back."""
+        if not self.config.is_distributed:
+            return dataloader
+        from torch.utils.data import DataLoader, Subset
+        if isinstance(dataloader, DataLoader):
+            idx = shard_indices(len(dataloader.dataset), self.config.rank, self.config.world_size)
+            return DataLoader(Subset(dataloader.dataset, idx), batch_size=dataloader.batch_size,
+                              shuffle=False, num_workers=dataloader.num_workers,
+                              collate_fn=dataloader.collate_fn, pin_memory=dataloader.pin_memory)
+        return self.shard_calibration(list(dataloader))
+
+    def quantize_layer_distributed(self, layer: torch.nn.Module, layer_inputs, quantization_config):
+        """One layer, every rank holding part of its inputs (reference
+        ``coordinator.py:183-235``): each rank accumulates the Hessian of its ``layer_inputs``,
+        the partial Hessians are summed over the ranks (``coordinator.py:224``), every rank
+        quantizes with the complete Hessian and ends with the same weights, and the stats are
+        returned.  ``quantization_config`` is the reference's dict (``bits``, ``group_size``,
+        optional ``actorder`` / ``percdamp`` / ``blocksize``) or a ``QuantizationConfig``.
+        Differences: no forward of the layer is run (its output is not used), and the sample
+        count is summed too, so shards of unequal size are weighted correctly (the reference
+        divides by the world size, which is right for equal shards only); the rank-0 broadcast
+        of ``coordinator.py:231-233`` is kept so that ranks cannot drift apart."""
+        from .gptq import GPTQ
+        cfg = quantization_config if isinstance(quantization_config, dict) else \
+            {k: getattr(quantization_config, k) for k in
+             ("bits", "group_size", "actorder", "percdamp", "blocksize")}
+        self.initialize()
+        gptq = GPTQ(layer, bits=cfg["bits"], group_size=cfg["group_size"],
+                    actorder=cfg.get("actorder", False), percdamp=cfg.get("percdamp", 0.01),
+                    blocksize=cfg.get("blocksize", 128), device=self.device)
+        for inp in layer_inputs:
+            gptq.add_batch(inp.to(self.device), None)
+        if self.comm.active:
+            if gptq._Hbuf is None:      # an empty shard still takes part in the sum
+                K8 = (gptq.columns + 7) // 8 * 8
+                gptq._Hbuf = torch.zeros((K8, K8), dtype=torch.float32, device=self.device)
+            self.comm.all_reduce_tensor(gptq._Hbuf)
+            n = torch.tensor([float(gptq.nsamples)], device=self.device)
+            self.comm.all_reduce_tensor(n)
+            gptq.nsamples = int(n.item())
+        stats = gptq.quantize()
+        self.last_gptq = gptq       # codes / scale / zero / g_idx for pack_weights()
+        if self.comm.active:
+            for _, param in layer.named_parameters():
+                self.comm.broadcast_tensor(param.data, src=0)
+        return stats
+
     # -- the exchange step ------------------------------------------------------------------
     def exchange_hessians(self, hessians: Dict[str, torch.Tensor], owners: Dict[str, int]) -> None:
         """Sums every partial Hessian over the ranks: onto its owner (``hessian_exchange ==

@@ -20,6 +20,23 @@ bool dgq_use_pdl() {
   return on;
 }
 
+int dgq_sm_count() {
+  static std::mutex mu;
+  static int cached[DGQ_MAX_DEVICES] = {};
+  const int dev = dgq_current_device();
+  if (dev < 0) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      return 148;
+    }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 DGQ_EXPORT int64_t dgq_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 DGQ_EXPORT int32_t dgq_version(void) { return 100; }
@@ -39,20 +56,18 @@ DGQ_EXPORT const char* dgq_status_string(int32_t status) {
 }
 
 DGQ_EXPORT int32_t dgq_device_check(void) {
-  static int cached_dev = -1;
-  static int32_t cached = DGQ_ERR_ARCH;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return DGQ_ERR_ARCH;
+  static std::mutex mu;
+  static int8_t known[DGQ_MAX_DEVICES] = {};   // 0 = not asked yet, 1 = sm_10x, 2 = other
+  const int dev = dgq_current_device();
+  if (dev < 0) return DGQ_ERR_ARCH;
+  std::lock_guard<std::mutex> lock(mu);
+  if (known[dev] == 0) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return DGQ_ERR_ARCH;
+    }
+    known[dev] = (major == 10) ? 1 : 2;
   }
-  if (dev == cached_dev) return cached;
-  int major = 0;
-  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return DGQ_ERR_ARCH;
-  }
-  cached_dev = dev;
-  cached = (major == 10) ? DGQ_OK : DGQ_ERR_ARCH;
-  return cached;
+  return known[dev] == 1 ? DGQ_OK : DGQ_ERR_ARCH;
 }

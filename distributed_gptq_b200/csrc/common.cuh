@@ -6,6 +6,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "dgq.h"
 
 #define DGQ_EXPORT extern "C" __attribute__((visibility("default")))
@@ -74,19 +76,45 @@ static inline bool dgq_aligned(const void* p, uintptr_t a) {
 
 static inline int64_t dgq_cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-// Number of SMs of the current device (148 on B200); cached per process.
-static inline int dgq_sm_count() {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      cached = n;
-    else
-      return 148;
+// ---- per-device state ----------------------------------------------------------------------
+// Function attributes (the dynamic shared-memory limit), occupancy figures and the SM count
+// belong to a device, and one process may drive several (one host thread per GPU, or one
+// thread that switches devices).  Everything cached is therefore indexed by the current
+// device and guarded by a mutex, since entry points may be called from several host threads.
+constexpr int DGQ_MAX_DEVICES = 64;
+
+static inline int dgq_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
   }
-  return cached;
+  return (dev >= 0 && dev < DGQ_MAX_DEVICES) ? dev : -1;
 }
+
+// Runs `setup` (a callable returning true on success) at most once per device, with that
+// device current; returns false if the device is unknown or the set-up failed (it is then
+// tried again by the next call).
+struct DgqDeviceOnce {
+  std::mutex mu;
+  bool done[DGQ_MAX_DEVICES] = {};
+  template <typename F>
+  bool run(F&& setup) {
+    const int dev = dgq_current_device();
+    if (dev < 0) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[dev]) return true;
+    if (!setup()) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    done[dev] = true;
+    return true;
+  }
+};
+
+// Number of SMs of the current device (148 on B200); looked up once per device (abi.cu).
+int dgq_sm_count();
 
 // Grid for a grid-stride kernel: enough CTAs to fill the machine a few times
 // over, rounded to a multiple of the SM count, never more than the work needs.

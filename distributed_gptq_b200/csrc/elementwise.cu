@@ -133,25 +133,39 @@ rtn_dequantize_kernel(const uint8_t* __restrict__ q, int64_t n, int group_size,
   }
 }
 
+// perm[i], or i itself when there is no permutation or the entry is not a valid index (a
+// caller's array that is not a permutation must not turn into an out-of-bounds access).
+__device__ __forceinline__ int checked_index(const int32_t* __restrict__ perm, int i, int n) {
+  if (!perm) return i;
+  const int p = perm[i];
+  return ((unsigned)p < (unsigned)n) ? p : i;
+}
+
 // ---- act-order ---------------------------------------------------------------------
 // rank(i) = #{ j : d[j] > d[i]  or  (d[j] == d[i] and j < i) } is the position of i in
 // a stable descending sort.  The key is the prepared diagonal: d = scale*H_ii, with a
 // zero entry (dead column) replaced by 1, exactly what the damping step will see.
+// A NaN entry (calibration activations that went non-finite) compares false with everything
+// and would leave ranks unassigned, so the key maps NaN to +inf: with ties broken by index
+// the ranks are a permutation for every input.  (The inverse factor then reports such a
+// matrix as not positive definite.)
 // K <= ~16K, so the K^2 comparisons are spread over the grid with the diagonal staged
 // through shared memory.
+__device__ __forceinline__ float actorder_key(float d) {
+  if (d != d) return INFINITY;
+  return d == 0.f ? 1.f : d;
+}
+
 __global__ void __launch_bounds__(256)
 actorder_rank_kernel(const float* __restrict__ H, int64_t ldh, int K, float scale,
                      int32_t* __restrict__ perm, int32_t* __restrict__ invperm) {
   __shared__ float tile[256];
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  float di = (i < K) ? __fmul_rn(scale, H[(int64_t)i * ldh + i]) : 0.f;
-  if (di == 0.f) di = 1.f;
+  const float di = actorder_key((i < K) ? __fmul_rn(scale, H[(int64_t)i * ldh + i]) : 0.f);
   int rank = 0;
   for (int j0 = 0; j0 < K; j0 += 256) {
     int j = j0 + threadIdx.x;
-    float dj_own = (j < K) ? __fmul_rn(scale, H[(int64_t)j * ldh + j]) : -INFINITY;
-    if (dj_own == 0.f) dj_own = 1.f;
-    tile[threadIdx.x] = dj_own;
+    tile[threadIdx.x] = (j < K) ? actorder_key(__fmul_rn(scale, H[(int64_t)j * ldh + j])) : -INFINITY;
     __syncthreads();
     int lim = min(256, K - j0);
     for (int t = 0; t < lim; ++t) {
@@ -175,7 +189,7 @@ prepare_diag_kernel(const float* __restrict__ H, int64_t ldh, int K, float scale
                     float* __restrict__ diag_sum) {
   float local = 0.f;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < K; i += gridDim.x * blockDim.x) {
-    int p = perm ? perm[i] : i;
+    const int p = checked_index(perm, i, K);
     float d = __fmul_rn(scale, H[(int64_t)p * ldh + p]);
     bool is_dead = (d == 0.f);
     if (is_dead) d = 1.f;
@@ -198,8 +212,8 @@ prepare_gather_kernel(const float* __restrict__ H, int64_t ldh, float* __restric
        idx += (int64_t)gridDim.x * blockDim.x) {
     int i = (int)(idx / K);
     int j = (int)(idx - (int64_t)i * K);
-    int pi = perm ? perm[i] : i;
-    int pj = perm ? perm[j] : j;
+    const int pi = checked_index(perm, i, K);
+    const int pj = checked_index(perm, j, K);
     float v = __fmul_rn(scale, H[(int64_t)pi * ldh + pj]);
     if (i == j) {
       if (v == 0.f) v = 1.f;
@@ -218,7 +232,7 @@ permute_cols_f32_kernel(const float* __restrict__ src, int64_t lds, float* __res
        idx += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = idx / cols;
     int c = (int)(idx - r * cols);
-    int p = perm ? perm[c] : c;
+    const int p = checked_index(perm, c, cols);
     float v = src[r * lds + p];
     if (dead && dead[c]) v = 0.f;
     dst[r * ldd + c] = v;
@@ -233,7 +247,7 @@ permute_cols_u8_kernel(const uint8_t* __restrict__ src, int64_t lds, uint8_t* __
        idx += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = idx / cols;
     int c = (int)(idx - r * cols);
-    dst[r * ldd + c] = src[r * lds + perm[c]];
+    dst[r * ldd + c] = src[r * lds + checked_index(perm, c, cols)];
   }
 }
 

@@ -60,6 +60,7 @@ struct Params {
   int n_work;            // n_tiles * splits
   int64_t split_tokens;  // tokens per range, a multiple of BK
   int32_t* info;
+  int mirror;            // 1: also add the transposed tile below the diagonal
 };
 
 __device__ __forceinline__ void decode_work(const Params& p, int w, int& I, int& J, int64_t& t0,
@@ -230,10 +231,13 @@ hessian_syrk_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
             }
           }
           // mirrored element H[c][r]: consecutive lanes hold consecutive r -> coalesced
+          if (p.mirror) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (r < p.K && c0 + j < p.K)
-              tc05::red_add_f32(p.H + (int64_t)(c0 + j) * p.ldh + r, p.alpha * __uint_as_float(v[j]));
+            for (int j = 0; j < 32; ++j) {
+              if (r < p.K && c0 + j < p.K)
+                tc05::red_add_f32(p.H + (int64_t)(c0 + j) * p.ldh + r,
+                                  p.alpha * __uint_as_float(v[j]));
+            }
           }
         } else {
 #pragma unroll
@@ -242,7 +246,7 @@ hessian_syrk_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
             if (r < p.K && c < p.K && c >= r) {
               const float val = p.alpha * __uint_as_float(v[j]);
               tc05::red_add_f32(Hrow + c, val);
-              if (c > r) tc05::red_add_f32(p.H + (int64_t)c * p.ldh + r, val);
+              if (c > r && p.mirror) tc05::red_add_f32(p.H + (int64_t)c * p.ldh + r, val);
             }
           }
         }
@@ -293,9 +297,9 @@ int choose_splits(int n_tiles, int64_t T, int sms) {
 
 }  // namespace
 
-DGQ_EXPORT int32_t dgq_hessian_accum(const void* X, int64_t T, int32_t K, int64_t ldx, float* H,
-                                     int64_t ldh, float alpha, int32_t splits, int32_t* info,
-                                     void* stream) {
+namespace {
+int32_t hessian_accum(const void* X, int64_t T, int32_t K, int64_t ldx, float* H, int64_t ldh,
+                      float alpha, int32_t splits, int32_t* info, void* stream, int mirror) {
   DGQ_REQUIRE(X && H && T > 0 && K >= 8 && ldx >= K && ldh >= K && splits >= 0, DGQ_ERR_ARG);
   DGQ_REQUIRE(T < (1ll << 31), DGQ_ERR_SIZE);
   DGQ_REQUIRE(dgq_aligned(X, 16) && dgq_aligned(H, 16) && ldx % 8 == 0 && ldh % 4 == 0 && K % 8 == 0,
@@ -303,13 +307,12 @@ DGQ_EXPORT int32_t dgq_hessian_accum(const void* X, int64_t T, int32_t K, int64_
   int32_t arch = dgq_device_check();
   if (arch != DGQ_OK) return arch;
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(hessian_syrk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)SMEM_BYTES) != cudaSuccess)
-      return DGQ_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static DgqDeviceOnce once;
+  if (!once.run([] {
+        return cudaFuncSetAttribute(hessian_syrk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)SMEM_BYTES) == cudaSuccess;
+      }))
+    return DGQ_ERR_LAUNCH;
 
   CUtensorMap tmap;
   if (!tc05::make_tensor_map_2d(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, (uint64_t)T,
@@ -331,6 +334,7 @@ DGQ_EXPORT int32_t dgq_hessian_accum(const void* X, int64_t T, int32_t K, int64_
   s = (int)dgq_cdiv(T, p.split_tokens);  // drop ranges that would be empty
   p.n_work = p.n_tiles * s;
   p.info = info;
+  p.mirror = mirror;
 
   // Work items are dealt round robin, so the kernel lasts as long as the CTA with the most
   // items: the smallest grid with that many rounds is as fast as one CTA per SM and leaves
@@ -338,5 +342,49 @@ DGQ_EXPORT int32_t dgq_hessian_accum(const void* X, int64_t T, int32_t K, int64_
   const int64_t rounds = dgq_cdiv(p.n_work, sms);
   unsigned grid = (unsigned)dgq_cdiv(p.n_work, rounds);
   hessian_syrk_kernel<<<grid, THREADS, SMEM_BYTES, dgq_stream(stream)>>>(tmap, p);
+  return dgq_launch_status();
+}
+
+// Copies the part of H above the diagonal to below it (32 x 32 tiles through shared memory,
+// so that both the reads and the writes are coalesced).
+__global__ void __launch_bounds__(256)
+mirror_upper_kernel(float* __restrict__ H, int64_t ldh, int K) {
+  __shared__ float tile[32][33];
+  const int nt = (K + 31) / 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  for (int64_t t = blockIdx.x; t < (int64_t)nt * nt; t += gridDim.x) {
+    const int bi = (int)(t / nt), bj = (int)(t % nt);
+    if (bj < bi) continue;                                   // tiles on or above the diagonal
+    for (int y = ty; y < 32; y += 8) {
+      const int r = bi * 32 + y, c = bj * 32 + tx;
+      tile[y][tx] = (r < K && c < K) ? H[(int64_t)r * ldh + c] : 0.f;
+    }
+    __syncthreads();
+    for (int y = ty; y < 32; y += 8) {
+      const int r = bj * 32 + y, c = bi * 32 + tx;           // destination H[r][c] = source[c'][r']
+      if (r < K && c < K && r > c) H[(int64_t)r * ldh + c] = tile[tx][y];
+    }
+    __syncthreads();
+  }
+}
+}  // namespace
+
+DGQ_EXPORT int32_t dgq_hessian_accum(const void* X, int64_t T, int32_t K, int64_t ldx, float* H,
+                                     int64_t ldh, float alpha, int32_t splits, int32_t* info,
+                                     void* stream) {
+  return hessian_accum(X, T, K, ldx, H, ldh, alpha, splits, info, stream, 1);
+}
+
+DGQ_EXPORT int32_t dgq_hessian_accum_upper(const void* X, int64_t T, int32_t K, int64_t ldx,
+                                           float* H, int64_t ldh, float alpha, int32_t splits,
+                                           int32_t* info, void* stream) {
+  return hessian_accum(X, T, K, ldx, H, ldh, alpha, splits, info, stream, 0);
+}
+
+DGQ_EXPORT int32_t dgq_hessian_mirror(float* H, int32_t K, int64_t ldh, void* stream) {
+  DGQ_REQUIRE(H && K > 0 && ldh >= K, DGQ_ERR_ARG);
+  const int64_t nt = dgq_cdiv(K, 32);
+  const unsigned grid = (unsigned)std::min<int64_t>(nt * nt, (int64_t)dgq_sm_count() * 16);
+  mirror_upper_kernel<<<grid, 256, 0, dgq_stream(stream)>>>(H, ldh, K);
   return dgq_launch_status();
 }

@@ -369,7 +369,8 @@ struct Plan {
   float* T2[32];        // per recursion depth: the product T1 * X11
   int32_t* info;
   cudaStream_t st;      // the caller's stream
-  cudaStream_t side;    // takes T2 = T1 * X11, which nothing needs before the node's last product
+  cudaStream_t* side;   // per depth: takes T2 = T1 * X11, which nothing needs before the node's
+                        // last product
   cudaEvent_t* fork;    // per depth: T1 is ready (recorded on st)
   cudaEvent_t* join;    // per depth: T2 is ready (recorded on side)
   int64_t leaves;
@@ -379,12 +380,15 @@ struct Plan {
 // One side stream and one pair of events per recursion depth for every (device, caller
 // stream) this host thread has used, created on first use and kept for the life of the
 // thread: calls on different streams must not share a side stream, or they would wait for
-// each other's products.  The table is small; when it is full an entry is taken over (stream
+// each other's products.  Depths do not share one either: the small product of a node deep
+// in the second half of the recursion would queue behind its ancestor's large one, and the
+// node's last product waits for it.  The table is small; when it is full an entry is taken over (stream
 // order keeps that correct, it only couples the two callers).
+constexpr int SIDE_STREAMS = 10;
 struct SideResources {
   int device = -1;
   cudaStream_t caller = nullptr;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream[SIDE_STREAMS] = {};   // depth d uses stream[min(d, SIDE_STREAMS - 1)]
   cudaEvent_t fork[32] = {}, join[32] = {};
   bool ok = false;
 };
@@ -410,7 +414,12 @@ SideResources* side_resources(cudaStream_t caller) {
     return r;
   }
   if (!r->ok) {
-    if (cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    // same priority as the caller's stream: the side products are on the chain's critical path
+    int prio = 0;
+    if (cudaStreamGetPriority(caller, &prio) != cudaSuccess) prio = 0;
+    for (int d = 0; d < SIDE_STREAMS; ++d)
+      if (cudaStreamCreateWithPriority(&r->stream[d], cudaStreamNonBlocking, prio) != cudaSuccess)
+        return nullptr;
     for (int d = 0; d < 32; ++d) {
       if (cudaEventCreateWithFlags(&r->fork[d], cudaEventDisableTiming) != cudaSuccess ||
           cudaEventCreateWithFlags(&r->join[d], cudaEventDisableTiming) != cudaSuccess)
@@ -477,10 +486,11 @@ void rec(Plan& p, int o, int n, int depth) {
   mm(p, p.st, V21, ld, V11, ld, false, T1, h, m2, h, h, 1.f, 0.f, 0, 1, 0, 0);
   // T2 = T1 * X11 (X11[k][j] is non-zero for k >= j) runs beside the Schur complement and
   // the whole second half of the recursion
+  cudaStream_t side = p.side[std::min(depth, SIDE_STREAMS - 1)];
   cudaEventRecord(p.fork[depth], p.st);
-  cudaStreamWaitEvent(p.side, p.fork[depth], 0);
-  mm(p, p.side, T1, h, V11, ld, true, T2, h, m2, h, h, 1.f, 0.f, 1, 0, 0, 0);
-  cudaEventRecord(p.join[depth], p.side);
+  cudaStreamWaitEvent(side, p.fork[depth], 0);
+  mm(p, side, T1, h, V11, ld, true, T2, h, m2, h, h, 1.f, 0.f, 1, 0, 0, 0);
+  cudaEventRecord(p.join[depth], side);
   // V22 -= T1 * T1^T, lower part
   mm(p, p.st, T1, h, T1, h, false, V22, ld, m2, m2, h, -1.f, 1.f, 0, 0, 0, 1);
   rec(p, o + h, m2, depth + 1);
@@ -507,13 +517,12 @@ DGQ_EXPORT int32_t dgq_inv_chol_upper(float* A, int32_t K, int64_t lda, int32_t*
   DGQ_REQUIRE(A && ws && K > 0 && lda >= K, DGQ_ERR_ARG);
   DGQ_REQUIRE(ws_bytes >= dgq_inv_chol_workspace_bytes(K), DGQ_ERR_WORKSPACE);
   DGQ_REQUIRE(dgq_aligned(A, 16) && dgq_aligned(ws, 16), DGQ_ERR_ALIGN);
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(leaf_inv_chol_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(LEAF_SMEM_FLOATS * sizeof(float))) != cudaSuccess)
-      return DGQ_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static DgqDeviceOnce once;
+  if (!once.run([] {
+        return cudaFuncSetAttribute(leaf_inv_chol_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)(LEAF_SMEM_FLOATS * sizeof(float))) == cudaSuccess;
+      }))
+    return DGQ_ERR_LAUNCH;
   Plan p;
   p.st = dgq_stream(stream);
   p.K = K;

@@ -568,16 +568,24 @@ bool launch_mma_typed(const LinArgs& a, int m0, cudaStream_t st) {
   // 16-feature tiles (to within one)
   const int n_tiles = (int)dgq_cdiv(a.N_out, 16);
   const bool two = a.M - m0 > 8;
-  static int resident[2] = {0, 0};
-  if (resident[two] == 0) {
-    int per_sm = 0;
-    const cudaError_t e = two
-        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qlinear_mma_kernel<T, 2>, MMA_WARPS * 32, 0)
-        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qlinear_mma_kernel<T, 1>, MMA_WARPS * 32, 0);
-    if (e != cudaSuccess || per_sm <= 0) return false;
-    resident[two] = per_sm * dgq_sm_count();
+  static std::mutex mu;
+  static int resident_of[DGQ_MAX_DEVICES][2] = {};   // per device: occupancy differs with the part
+  const int dev = dgq_current_device();
+  if (dev < 0) return false;
+  int resident;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (resident_of[dev][two] == 0) {
+      int per_sm = 0;
+      const cudaError_t e = two
+          ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qlinear_mma_kernel<T, 2>, MMA_WARPS * 32, 0)
+          : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qlinear_mma_kernel<T, 1>, MMA_WARPS * 32, 0);
+      if (e != cudaSuccess || per_sm <= 0) return false;
+      resident_of[dev][two] = per_sm * dgq_sm_count();
+    }
+    resident = resident_of[dev][two];
   }
-  const int rounds = (int)dgq_cdiv(n_tiles, resident[two]);
+  const int rounds = (int)dgq_cdiv(n_tiles, resident);
   const unsigned grid = (unsigned)dgq_cdiv(n_tiles, rounds);
   if (two) qlinear_mma_kernel<T, 2><<<grid, MMA_WARPS * 32, 0, st>>>(a, m0, n_tiles);
   else qlinear_mma_kernel<T, 1><<<grid, MMA_WARPS * 32, 0, st>>>(a, m0, n_tiles);

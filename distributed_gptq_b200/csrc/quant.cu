@@ -40,6 +40,7 @@ struct QuantArgs {
   float* err;            // (N_out, err_ld): scaled errors of the current super-block
   int64_t err_ld; int err_off;  // row stride and first column of the current block in it
   double* total_error;
+  double* row_error;     // optional (N_out): sum of squared scaled errors of every row
   int N_out, K, i1, bw;  // block start and width
   int group;             // effective group size (K for per-channel)
   float maxq;
@@ -188,6 +189,7 @@ gptq_block_kernel(const QuantArgs a) {
     // ---- outputs
     float* erow = a.err + (int64_t)row * a.err_ld + a.err_off;
     uint8_t* crow = a.codes + (int64_t)row * a.ldc + a.i1;
+    double row_sq = 0.0;
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       int c = t * 32 + lane;
@@ -195,8 +197,14 @@ gptq_block_kernel(const QuantArgs a) {
         wrow[c] = what[t];
         crow[c] = (uint8_t)code[t];
         erow[c] = ev[t];
-        err_sq += (double)ev[t] * (double)ev[t];
+        row_sq += (double)ev[t] * (double)ev[t];
       }
+    }
+    err_sq += row_sq;
+    if (a.row_error) {   // one warp per row and one launch per block: no other writer
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) row_sq += __shfl_xor_sync(0xffffffffu, row_sq, o);
+      if (lane == 0) a.row_error[row] += row_sq;
     }
   }
 #pragma unroll
@@ -319,6 +327,7 @@ gptq_block8_kernel(const QuantArgs a) {
       }
     }
     // ---- outputs
+    double row_sq = 0.0;
     if (live) {
       float* erow = a.err + (int64_t)row * a.err_ld + a.err_off;
       uint8_t* crow = a.codes + (int64_t)row * a.ldc + a.i1;
@@ -331,8 +340,14 @@ gptq_block8_kernel(const QuantArgs a) {
             make_float4(ev[4 * i], ev[4 * i + 1], ev[4 * i + 2], ev[4 * i + 3]);
         *reinterpret_cast<uint32_t*>(crow + c) = code[i];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) err_sq += (double)ev[4 * i + e] * (double)ev[4 * i + e];
+        for (int e = 0; e < 4; ++e) row_sq += (double)ev[4 * i + e] * (double)ev[4 * i + e];
       }
+    }
+    err_sq += row_sq;
+    if (a.row_error) {   // eight lanes per row and one launch per block: no other writer
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) row_sq += __shfl_xor_sync(0xffffffffu, row_sq, o);
+      if (live && sub == 0) a.row_error[row] += row_sq;
     }
   }
 #pragma unroll
@@ -356,6 +371,16 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
                                      int32_t blocksize, uint8_t* codes, int64_t ldc, float* scales,
                                      float* zeros, double* total_error, void* ws, int64_t ws_bytes,
                                      void* stream) {
+  return dgq_gptq_quantize_rows(W, ldw, U, ldu, N_out, K, bits, group_size, blocksize, codes, ldc,
+                                scales, zeros, total_error, nullptr, ws, ws_bytes, stream);
+}
+
+DGQ_EXPORT int32_t dgq_gptq_quantize_rows(float* W, int64_t ldw, const float* U, int64_t ldu,
+                                          int32_t N_out, int32_t K, int32_t bits,
+                                          int32_t group_size, int32_t blocksize, uint8_t* codes,
+                                          int64_t ldc, float* scales, float* zeros,
+                                          double* total_error, double* row_error, void* ws,
+                                          int64_t ws_bytes, void* stream) {
   DGQ_REQUIRE(W && U && codes && scales && zeros && total_error && ws, DGQ_ERR_ARG);
   DGQ_REQUIRE(N_out > 0 && K > 0 && ldw >= K && ldu >= K && ldc >= K && valid_bits(bits), DGQ_ERR_ARG);
   DGQ_REQUIRE(blocksize > 0 && blocksize <= MAX_BLOCK, DGQ_ERR_UNSUPPORTED);
@@ -371,17 +396,16 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   DGQ_REQUIRE(dgq_aligned(ws, 16), DGQ_ERR_ALIGN);
   cudaStream_t st = dgq_stream(stream);
 
-  static bool attr_set = false;
-  const size_t smem = (size_t)MAX_BLOCK * MAX_BLOCK * sizeof(float);
-  if (!attr_set) {
-    const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
-    if (cudaFuncSetAttribute(gptq_block_kernel, at, (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(gptq_block8_kernel<1>, at, (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(gptq_block8_kernel<2>, at, (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(gptq_block8_kernel<4>, at, (int)smem) != cudaSuccess)
-      return DGQ_ERR_LAUNCH;
-    attr_set = true;
-  }
+  constexpr size_t smem = (size_t)MAX_BLOCK * MAX_BLOCK * sizeof(float);
+  static DgqDeviceOnce once;
+  if (!once.run([] {
+        const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        return cudaFuncSetAttribute(gptq_block_kernel, at, (int)smem) == cudaSuccess &&
+               cudaFuncSetAttribute(gptq_block8_kernel<1>, at, (int)smem) == cudaSuccess &&
+               cudaFuncSetAttribute(gptq_block8_kernel<2>, at, (int)smem) == cudaSuccess &&
+               cudaFuncSetAttribute(gptq_block8_kernel<4>, at, (int)smem) == cudaSuccess;
+      }))
+    return DGQ_ERR_LAUNCH;
   // the fast kernel takes full 128-column blocks with 16-byte aligned rows
   const bool fast_layout = blocksize == MAX_BLOCK && ldw % 4 == 0 && ldu % 4 == 0 && ldc % 4 == 0 &&
                            dgq_aligned(W, 16) && dgq_aligned(U, 16) && dgq_aligned(codes, 4);
@@ -390,6 +414,9 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   else if (group == 64) gpb = 2;
   else if (group == 32) gpb = 4;
   if (cudaMemsetAsync(total_error, 0, sizeof(double), st) != cudaSuccess) return DGQ_ERR_LAUNCH;
+  if (row_error &&
+      cudaMemsetAsync(row_error, 0, sizeof(double) * (size_t)N_out, st) != cudaSuccess)
+    return DGQ_ERR_LAUNCH;
 
   QuantArgs a;
   a.W = W; a.ldw = ldw; a.U = U; a.ldu = ldu; a.codes = codes; a.ldc = ldc;
@@ -397,6 +424,7 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   a.n_groups = per_channel ? 1 : (int)dgq_cdiv(K, group);
   a.err = reinterpret_cast<float*>(ws);
   a.total_error = total_error;
+  a.row_error = row_error;
   a.N_out = N_out; a.K = K; a.group = group; a.maxq = (float)((1 << bits) - 1);
   const unsigned grid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, ROWS_PER_CTA),
                                                     (int64_t)dgq_sm_count() * 2);
@@ -408,6 +436,14 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
   int super_cols = (int)std::min<int64_t>(SUPER_BLOCK, ws_bytes / ((int64_t)N_out * sizeof(float)));
   super_cols = std::max(MAX_BLOCK, super_cols / MAX_BLOCK * MAX_BLOCK);
   super_cols = super_cols / blocksize * blocksize;  // block boundaries stay multiples of blocksize
+  // A group wider than a block takes its min/max over all its columns when its first column
+  // is reached, so by then every one of them must have received all earlier updates: the
+  // group either lies inside one super-block or starts where a super-block starts.
+  if (!per_channel && group > blocksize) {
+    if (group <= super_cols) super_cols = super_cols / group * group;
+    else
+      while (group % super_cols != 0) super_cols -= blocksize;   // ends at blocksize at the latest
+  }
   a.err_ld = super_cols;
   // W[:, c0:c1] -= Err[:, e0:e0+k] * U[r0:r0+k, c0:c1]
   auto update = [&](int e0, int k, int r0, int c0, int c1) {
@@ -438,12 +474,15 @@ DGQ_EXPORT int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int6
         const unsigned fgrid = (unsigned)std::min<int64_t>(dgq_cdiv(N_out, F_ROWS_PER_CTA),
                                                            (int64_t)dgq_sm_count() * 3);
         const dim3 fg(fgrid), fb(F_WARPS * 32);
-        if (gpb == 1) dgq_launch_chained(gptq_block8_kernel<1>, fg, fb, smem, st, a);
-        else if (gpb == 2) dgq_launch_chained(gptq_block8_kernel<2>, fg, fb, smem, st, a);
-        else dgq_launch_chained(gptq_block8_kernel<4>, fg, fb, smem, st, a);
+        cudaError_t e;
+        if (gpb == 1) e = dgq_launch_chained(gptq_block8_kernel<1>, fg, fb, smem, st, a);
+        else if (gpb == 2) e = dgq_launch_chained(gptq_block8_kernel<2>, fg, fb, smem, st, a);
+        else e = dgq_launch_chained(gptq_block8_kernel<4>, fg, fb, smem, st, a);
+        if (e != cudaSuccess) return DGQ_ERR_LAUNCH;
       } else {
-        dgq_launch_chained(gptq_block_kernel, dim3(grid), dim3(ROWS_PER_CTA * 32),
-                           (size_t)a.bw * MAX_BLOCK * sizeof(float), st, a);
+        if (dgq_launch_chained(gptq_block_kernel, dim3(grid), dim3(ROWS_PER_CTA * 32),
+                               (size_t)a.bw * MAX_BLOCK * sizeof(float), st, a) != cudaSuccess)
+          return DGQ_ERR_LAUNCH;
       }
       update(a.err_off, a.bw, i1, i1 + a.bw, s1);      // rest of this super-block
     }

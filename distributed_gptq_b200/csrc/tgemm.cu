@@ -399,15 +399,13 @@ bool tgemm_supported(const TGemmArgs& g) {
 }
 
 bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(tgemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)SMEM_BYTES) != cudaSuccess ||
-        cudaFuncSetAttribute(tgemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)SMEM_BYTES) != cudaSuccess)
-      return false;
-    attr_set = true;
-  }
+  static DgqDeviceOnce once;
+  if (!once.run([] {
+        const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        return cudaFuncSetAttribute(tgemm_kernel<false>, at, (int)SMEM_BYTES) == cudaSuccess &&
+               cudaFuncSetAttribute(tgemm_kernel<true>, at, (int)SMEM_BYTES) == cudaSuccess;
+      }))
+    return false;
   CUtensorMap map_a, map_b;
   if (!tc05::make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.a, (uint64_t)g.m,
                                 (uint64_t)g.k, (uint64_t)g.lda * 4, TILE, BK))

@@ -7,7 +7,7 @@ every computation done by the sm_100a kernels behind ``libdgq.so``.
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Optional
+from typing import Any, Dict, List, Optional
 
 import torch
 import torch.nn as nn
@@ -91,6 +91,10 @@ class GPTQ:
         self.columns = self._weight_matrix().shape[1]
         self._info = None
         self._pending = None
+        # add_batch updates only the part of the Hessian on and above the diagonal (half the
+        # reduction traffic of every batch); the lower part is filled in when the matrix is
+        # read: by the `H` property and before quantization
+        self._lower_stale = False
 
     # ------------------------------------------------------------------ helpers
     def _weight_matrix(self) -> torch.Tensor:
@@ -103,7 +107,13 @@ class GPTQ:
     def H(self) -> Optional[torch.Tensor]:
         if self._Hbuf is None:
             return None
+        self._complete_hessian()
         return self._Hbuf[:self.columns, :self.columns]
+
+    def _complete_hessian(self) -> None:
+        if self._lower_stale and self._Hbuf is not None:
+            _C.hessian_mirror(self._Hbuf)
+            self._lower_stale = False
 
     @H.setter
     def H(self, value: Optional[torch.Tensor]) -> None:
@@ -116,6 +126,7 @@ class GPTQ:
         buf = torch.zeros((K8, K8), dtype=torch.float32, device=self.device)
         buf[:K, :K] = value.to(self.device, torch.float32)
         self._Hbuf = buf
+        self._lower_stale = False
 
     def _tokens(self, inp: torch.Tensor) -> torch.Tensor:
         """Flattens a batch to ``(tokens, columns)`` the way the layer consumes it."""
@@ -151,7 +162,8 @@ class GPTQ:
         xb = _C.to_bf16(x)
         self.nsamples += batch
         if xb.shape[0] > 0:
-            _C.hessian_accum(xb, self._Hbuf, 1.0, 0, self._info)
+            _C.hessian_accum(xb, self._Hbuf, 1.0, 0, self._info, upper_only=True)
+            self._lower_stale = True
 
     # ------------------------------------------------------------------ quantize
     def quantize(self) -> Dict[str, Any]:
@@ -170,51 +182,7 @@ class GPTQ:
         current CUDA stream and returns without waiting for the device, so that a caller can
         put the chains of independent layers on different streams (see ``streams.ChainPool``)
         or keep accumulating other Hessians meanwhile.  :meth:`quantize_finish` must follow."""
-        if self._Hbuf is None or self.nsamples == 0:
-            raise RuntimeError("no calibration data: call add_batch before quantize")
-        cur = torch.cuda.current_stream(self.device)
-        Wm = self._weight_matrix()
-        N_out, K = Wm.shape
-        # the inputs may have been produced on another stream than the one this chain runs on
-        self._Hbuf.record_stream(cur)
-        if Wm.is_cuda:
-            Wm.record_stream(cur)
-        W = Wm.to(self.device, torch.float32).contiguous().clone()
-        H = self.H
-        scale = float(torch.tensor(2.0 / self.nsamples, dtype=torch.float32))
-
-        perm = invperm = None
-        if self.actorder:
-            perm, invperm = _C.actorder_perm(H, scale)
-        Hp, dead = _C.hessian_prepare(H, scale, self.percdamp, perm)
-        Wp = _C.permute_cols(W, perm, dead)
-        info = _C.new_info(self.device)
-        U = _C.inv_chol_upper(Hp, info)
-        codes, scales, zeros, terr = _C.gptq_quantize(Wp, U, self.bits, self.group_size,
-                                                      self.blocksize)
-        g = K if (self.group_size <= 0 or self.group_size >= K) else self.group_size
-        if self.actorder:
-            Q = _C.permute_cols(Wp, invperm)
-            codes = _C.permute_cols(codes, invperm)
-            g_idx = (invperm // g).to(torch.int32)
-        else:
-            Q = Wp
-            g_idx = (torch.arange(K, device=self.device, dtype=torch.int32) // g)
-        old_weight = self.layer.weight.data
-        self.codes, self.scale, self.zero, self.g_idx, self.perm = codes, scales, zeros, g_idx, perm
-        self.layer.weight.data = Q.reshape(self.layer.weight.shape).to(
-            device=self.layer.weight.device, dtype=self.layer.weight.dtype)
-        # the status words and the error sum travel to pinned host memory on this stream, so that
-        # quantize_finish only has to wait for this chain, not for the stream it is called on
-        def to_host(t):
-            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
-            h.copy_(t, non_blocking=True)
-            return h
-        status = {"info": to_host(info), "terr": to_host(terr),
-                  "hessian_info": to_host(self._info) if self._info is not None else None}
-        done = torch.cuda.Event()
-        done.record(cur)
-        self._pending = {"status": status, "old_weight": old_weight, "done": done}
+        quantize_group_launch([self])
 
     def quantize_finish(self) -> Dict[str, Any]:
         """Second half of :meth:`quantize`: waits for the chain, raises if the Hessian
@@ -239,7 +207,7 @@ class GPTQ:
             self.layer.weight.data = pend["old_weight"]
             self.codes = self.scale = self.zero = self.g_idx = self.perm = None
             raise
-        total_error = float(status["terr"].item())
+        total_error = float(status["terr"][pend["slot"]].item())
         return {
             "bits": self.bits,
             "group_size": self.group_size,
@@ -293,6 +261,91 @@ class GPTQ:
     def free(self) -> None:
         self.free_hessian()
         torch.cuda.empty_cache()
+
+
+def quantize_group_launch(members: List["GPTQ"]) -> Dict[str, torch.Tensor]:
+    """Enqueues the quantization of several layers that read the same input tensor (q/k/v or
+    gate/up of a decoder block) as one chain on the current stream.
+
+    ``members[0]`` holds the Hessian.  The Hessian fixes the column order, the damped inverse
+    factor ``U`` and nothing else, and the rows of a weight matrix are quantized independently
+    given ``U`` (reference ``core/gptq.py:131-194`` has no term that couples rows), so the
+    members' weights are stacked into one ``(sum N_out, K)`` matrix: one preparation, one
+    inverse factor and one pass of the block loop serve all of them, with results equal to
+    quantizing each layer by itself.  Every member ends in the state
+    :meth:`GPTQ.quantize_launch` leaves it in; :meth:`GPTQ.quantize_finish` must follow for
+    each.  Returns device tensors a caller may ship before the host has seen them:
+    ``info`` / ``hessian_info`` (2 x int32 status words) and ``terr`` (one double per
+    member)."""
+    lead = members[0]
+    if lead._Hbuf is None or lead.nsamples == 0:
+        raise RuntimeError("no calibration data: call add_batch before quantize")
+    dev = lead.device
+    K = lead.columns
+    for m in members[1:]:
+        if (m.columns, m.bits, m.group_size, m.actorder, m.percdamp, m.blocksize, m.device) != \
+                (K, lead.bits, lead.group_size, lead.actorder, lead.percdamp, lead.blocksize, dev):
+            raise ValueError("layers quantized as one group must agree in input width and settings")
+    cur = torch.cuda.current_stream(dev)
+    # the inputs may have been produced on another stream than the one this chain runs on
+    lead._Hbuf.record_stream(cur)
+    # the accumulation (and a reduction over ranks) only kept the upper triangle up to date
+    _C.hessian_mirror(lead._Hbuf)
+    lead._lower_stale = False
+    parts, bounds, r = [], [], 0
+    for m in members:
+        Wm = m._weight_matrix()
+        if Wm.is_cuda:
+            Wm.record_stream(cur)
+        parts.append(Wm.to(dev, torch.float32))
+        bounds.append((r, r + Wm.shape[0]))
+        r += Wm.shape[0]
+    W = torch.cat(parts) if len(parts) > 1 else parts[0].contiguous().clone()
+    del parts
+    H = lead.H
+    scale = float(torch.tensor(2.0 / lead.nsamples, dtype=torch.float32))
+
+    perm = invperm = None
+    if lead.actorder:
+        perm, invperm = _C.actorder_perm(H, scale)
+    Hp, dead = _C.hessian_prepare(H, scale, lead.percdamp, perm)
+    Wp = _C.permute_cols(W, perm, dead)
+    del W
+    info = _C.new_info(dev)
+    U = _C.inv_chol_upper(Hp, info)
+    codes, scales, zeros, rerr = _C.gptq_quantize(Wp, U, lead.bits, lead.group_size,
+                                                  lead.blocksize, row_error=True)
+    g = K if (lead.group_size <= 0 or lead.group_size >= K) else lead.group_size
+    if lead.actorder:
+        Q = _C.permute_cols(Wp, invperm)
+        codes = _C.permute_cols(codes, invperm)
+        g_idx = (invperm // g).to(torch.int32)
+    else:
+        Q = Wp
+        g_idx = (torch.arange(K, device=dev, dtype=torch.int32) // g)
+    terr = torch.stack([rerr[a:b].sum() for a, b in bounds])
+
+    # the status words and the error sums travel to pinned host memory on this stream, so that
+    # quantize_finish only has to wait for this chain, not for the stream it is called on
+    def to_host(t):
+        h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        h.copy_(t, non_blocking=True)
+        return h
+    hinfo = lead._info
+    status = {"info": to_host(info), "terr": to_host(terr),
+              "hessian_info": to_host(hinfo) if hinfo is not None else None}
+    for slot, (m, (a, b)) in enumerate(zip(members, bounds)):
+        old_weight = m.layer.weight.data
+        m.codes, m.scale, m.zero, m.g_idx, m.perm = codes[a:b], scales[a:b], zeros[a:b], g_idx, perm
+        m.layer.weight.data = Q[a:b].reshape(m.layer.weight.shape).to(
+            device=m.layer.weight.device, dtype=m.layer.weight.dtype)
+        m._pending = {"status": status, "old_weight": old_weight, "slot": slot}
+    done = torch.cuda.Event()
+    done.record(cur)
+    for m in members:
+        m._pending["done"] = done
+    return {"info": info, "hessian_info": hinfo if hinfo is not None else torch.zeros_like(info),
+            "terr": terr}
 
 
 def quantize_layer_gptq(layer: nn.Module, calibration_data, bits: int = 4, group_size: int = 128,

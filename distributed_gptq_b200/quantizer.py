@@ -1,20 +1,37 @@
 """Model-level driver: ``QuantizationConfig``, ``DistributedGPTQuantizer`` and
 ``quantize_model_simple`` (reference ``src/distributed_gptq/core/quantizer.py``).
 
-Differences in mechanism, not in interface: Hessians are accumulated inside the forward
-hooks (the reference stores every layer's inputs on the host first,
-``core/quantizer.py:194-246``); layers that receive the same input tensor share one
-Hessian; with several ranks the calibration sequences are split, partial Hessians are
-reduced to the rank that owns a layer and layers are quantized in parallel across ranks.
+Differences in mechanism, not in interface:
+
+* Hessians are accumulated inside forward hooks (the reference stores every layer's inputs
+  on the host first, ``core/quantizer.py:194-246``); layers that receive the same input
+  tensor share one Hessian and are quantized as one stacked matrix.
+* A model whose quantized layers sit in a ``ModuleList`` of blocks applied one after the
+  other (every decoder-only transformer) is calibrated block by block: the inputs of the
+  first block are captured once, then every block is run over all calibration batches and
+  its outputs are kept as the next block's inputs.  A block's Hessians are therefore
+  complete when its pass ends, and their exchange between ranks, the damped inverse and the
+  block quantization of that block run on side streams while the next block's pass keeps
+  the tensor cores busy; only one or two blocks' Hessians are alive at a time.  Other models
+  take one whole-model pass per batch and quantize afterwards.
+* With several ranks the calibration sequences are split, partial Hessians are reduced to
+  the rank that owns a layer group, owners quantize in parallel and every block's results
+  travel in one flat buffer per owner.
+* ``true_sequential=True`` re-runs every block with its quantized weights before the next
+  block is calibrated (what the reference's CLI flag ``--true-sequential`` promises,
+  ``cli.py:207-211``); ``checkpoint_dir`` writes one shard per finished block and skips the
+  blocks already present when the run is repeated (``README.md:18``).
 """
 from __future__ import annotations
 
+import inspect
 import json
 import logging
+import os
 import time
 from dataclasses import asdict, dataclass
 from pathlib import Path
-from typing import Callable, Dict, Iterable, List, Optional, Union
+from typing import Callable, Dict, Iterable, List, Optional, Tuple, Union
 
 import torch
 import torch.nn as nn
@@ -22,7 +39,7 @@ import torch.nn as nn
 from . import _C, io
 from .coordinator import (DistributedConfig, DistributedGPTQCoordinator, assign_owners,
                           create_distributed_config, layer_cost)
-from .gptq import GPTQ
+from .gptq import GPTQ, quantize_group_launch
 from .streams import ChainPool
 
 logger = logging.getLogger(__name__)
@@ -31,7 +48,9 @@ logger = logging.getLogger(__name__)
 @dataclass
 class QuantizationConfig:
     """Reference ``core/quantizer.py:24-40``.  ``group_size = -1`` (one scale/zero per output
-    channel) is accepted in addition; ``use_triton`` is accepted and ignored."""
+    channel) is accepted in addition; ``use_triton`` is accepted and ignored.
+    ``true_sequential`` and ``checkpoint_dir`` are the two modes described in the module
+    docstring."""
     bits: int = 4
     group_size: int = 128
     actorder: bool = False
@@ -40,6 +59,8 @@ class QuantizationConfig:
     calibration_samples: int = 128
     use_triton: bool = False
     save_packed: bool = True
+    true_sequential: bool = False
+    checkpoint_dir: Optional[str] = None
 
     def validate(self):
         assert self.bits in [2, 3, 4, 8], f"Bits must be 2, 3, 4, or 8, got {self.bits}"
@@ -91,17 +112,73 @@ def _same_shape(a, b) -> bool:
     return a.shape == b.shape
 
 
+def make_batches(samples: List, batch_size: int) -> List:
+    """Consecutive samples of equal shape are merged, up to ``batch_size`` per batch."""
+    out, i = [], 0
+    while i < len(samples):
+        j = i + 1
+        while j < len(samples) and j - i < batch_size and _same_shape(samples[i], samples[j]):
+            j += 1
+        out.append(_merge(samples[i:j]))
+        i = j
+    return out
+
+
+class _StopForward(Exception):
+    """Raised by a hook to leave a forward pass that has delivered what was wanted."""
+
+
+def find_blocks(model: nn.Module, layers: Dict[str, nn.Module]) -> Optional[Tuple[str, nn.ModuleList]]:
+    """The ``ModuleList`` (two entries or more) that contains the most of ``layers``, with its
+    name; ``None`` if no list contains any."""
+    best, best_count = None, 0
+    for name, mod in model.named_modules():
+        if isinstance(mod, nn.ModuleList) and len(mod) >= 2:
+            prefix = name + "." if name else ""
+            count = sum(1 for n in layers
+                        if n.startswith(prefix) and n[len(prefix):].split(".", 1)[0].isdigit())
+            if count > best_count:
+                best, best_count = (name, mod), count
+    return best
+
+
+def _align(n: int, a: int = 16) -> int:
+    return (n + a - 1) // a * a
+
+
+class _Group:
+    """The layers of one block that share one Hessian, and what became of them."""
+
+    def __init__(self, leader: str, members: List[str], quantizers: Dict[str, GPTQ]):
+        self.leader = leader
+        self.members = members
+        self.q = [quantizers[m] for m in members]
+        self.owner = 0
+        self.mine = True
+        self.future = None          # chain enqueued -> (device status tensors, packed dicts)
+        self.reduce_work = None
+
+
 class DistributedGPTQuantizer:
     """Reference ``core/quantizer.py:43-355``."""
 
     def __init__(self, quantization_config: Optional[QuantizationConfig] = None,
                  distributed_config: Optional[DistributedConfig] = None,
-                 calibration_batch_size: int = 8):
+                 calibration_batch_size: int = 8, blockwise: Union[str, bool] = "auto",
+                 share_weights: bool = True):
         self.quant_config = quantization_config or QuantizationConfig()
         self.quant_config.validate()
         self.dist_config = distributed_config or create_distributed_config()
         self.coordinator = DistributedGPTQCoordinator(self.dist_config)
         self.calibration_batch_size = calibration_batch_size
+        # "auto": block by block when the model has a list of blocks (see find_blocks) and the
+        # replay of its first block reproduces the second block's input; False: always one
+        # whole-model pass per batch
+        self.blockwise = blockwise
+        # several ranks: ship the dequantized weights with the packed results, so that every
+        # rank ends with the same model (the reference's behaviour, coordinator.py:231-233);
+        # False leaves the weights of layers another rank quantized untouched on this rank
+        self.share_weights = share_weights
         self.quantized_layers: Dict[str, dict] = {}
         self.quantization_errors: Dict[str, float] = {}
         self.packed: Dict[str, Dict[str, torch.Tensor]] = {}
@@ -110,8 +187,13 @@ class DistributedGPTQuantizer:
         # diagnostics: when set before quantize_model, the reduced raw Hessian of every layer
         # this rank quantizes is kept (on the host) in `hessians`
         self.keep_hessians = False
+        # when set, CUDA events are recorded around the phases and summed into `timings`
+        self.profile = False
         self._pool: Optional[ChainPool] = None
+        self._share_stream: Optional[torch.cuda.Stream] = None
         self.hessians: Dict[str, torch.Tensor] = {}
+        self._leader: Dict[str, str] = {}
+        self.mode_used: Optional[str] = None
 
     # ------------------------------------------------------------------ discovery
     def _find_layers_to_quantize(self, model: nn.Module) -> Dict[str, nn.Module]:
@@ -123,24 +205,26 @@ class DistributedGPTQuantizer:
                 layers[name] = module
         return layers
 
-    # ------------------------------------------------------------------ calibration
-    @torch.no_grad()
-    def _accumulate_hessians(self, model: nn.Module, samples: List,
-                             layers: Dict[str, nn.Module]) -> Dict[str, GPTQ]:
-        cfg = self.quant_config
-        dev = self.coordinator.device
-        quantizers = {name: GPTQ(layer, bits=cfg.bits, group_size=cfg.group_size,
-                                 actorder=cfg.actorder, percdamp=cfg.percdamp,
-                                 blocksize=cfg.blocksize, device=dev)
-                      for name, layer in layers.items()}
-        leader: Dict[str, str] = {}     # layer -> layer whose Hessian it shares
-        seen: List = []                 # (input tensor, layer name) of the current forward
-        first = {"on": True}
+    # ------------------------------------------------------------------ hooks
+    def _new_quantizers(self, layers: Dict[str, nn.Module]) -> Dict[str, GPTQ]:
+        cfg, dev = self.quant_config, self.coordinator.device
+        return {name: GPTQ(layer, bits=cfg.bits, group_size=cfg.group_size, actorder=cfg.actorder,
+                           percdamp=cfg.percdamp, blocksize=cfg.blocksize, device=dev)
+                for name, layer in layers.items()}
+
+    def _hook_layers(self, layers: Dict[str, nn.Module], quantizers: Dict[str, GPTQ],
+                     state: dict):
+        """Forward pre-hooks that feed ``add_batch``.  During the first pass (``state["first"]``)
+        layers that receive the very same tensor are grouped under the first of them (its
+        ``leader``); only leaders accumulate.  ``state["accumulate"] = False`` makes a pass that
+        only discovers the grouping."""
+        leader: Dict[str, str] = state.setdefault("leader", {})
+        seen: List = state.setdefault("seen", [])
 
         def make_hook(name):
             def hook(module, args):
                 inp = args[0] if isinstance(args, tuple) else args
-                if first["on"]:
+                if state["first"]:
                     for t, owner in seen:
                         if (t.data_ptr() == inp.data_ptr() and t.shape == inp.shape and
                                 t.stride() == inp.stride() and t.dtype == inp.dtype):
@@ -149,31 +233,396 @@ class DistributedGPTQuantizer:
                     else:
                         leader[name] = name
                         seen.append((inp, name))   # holding the tensor keeps its address unique
-                if leader.get(name, name) == name:
+                if leader.get(name, name) == name and state.get("accumulate", True):
                     quantizers[name].add_batch(inp.detach(), None)
             return hook
 
-        handles = [layer.register_forward_pre_hook(make_hook(n)) for n, layer in layers.items()]
+        return [layer.register_forward_pre_hook(make_hook(n)) for n, layer in layers.items()]
+
+    def _to_device(self, batch):
+        dev = self.coordinator.device
+        if isinstance(batch, dict):
+            return {k: (v.to(dev, non_blocking=True) if torch.is_tensor(v) else v)
+                    for k, v in batch.items()}
+        return batch.to(dev, non_blocking=True)
+
+    def _run_model(self, model: nn.Module, batch, extra: dict):
+        batch = self._to_device(batch)
+        if isinstance(batch, dict):
+            return model(**{**extra, **batch})
+        return model(batch, **extra)
+
+    @staticmethod
+    def _forward_extras(model: nn.Module) -> dict:
+        """Keyword arguments added to every calibration forward: a model that can build a
+        key/value cache is told not to (it would hold every batch's keys and values)."""
         try:
-            i = 0
-            while i < len(samples):
-                j = i + 1
-                while (j < len(samples) and j - i < self.calibration_batch_size and
-                       _same_shape(samples[i], samples[j])):
-                    j += 1
-                batch = _merge(samples[i:j])
-                if isinstance(batch, dict):
-                    model(**{k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in batch.items()})
-                else:
-                    model(batch.to(dev))
-                seen.clear()
-                first["on"] = False
-                i = j
+            params = inspect.signature(model.forward).parameters
+        except (TypeError, ValueError):
+            return {}
+        return {"use_cache": False} if "use_cache" in params else {}
+
+    # ------------------------------------------------------------------ whole-model calibration
+    @torch.no_grad()
+    def _accumulate_hessians(self, model: nn.Module, batches: List,
+                             layers: Dict[str, nn.Module], discovery_batch=None) -> Dict[str, GPTQ]:
+        quantizers = self._new_quantizers(layers)
+        state = {"first": True}
+        extra = self._forward_extras(model)
+        handles = self._hook_layers(layers, quantizers, state)
+        try:
+            if not batches and discovery_batch is not None:
+                # this rank's shard is empty: one pass over a sample every rank has, so that the
+                # grouping (hence the order and size of the collectives) is the same everywhere
+                state["accumulate"] = False
+                self._run_model(model, discovery_batch, extra)
+                state["seen"].clear()
+                state["first"] = False
+            for batch in batches:
+                self._run_model(model, batch, extra)
+                state["seen"].clear()
+                state["first"] = False
         finally:
             for h in handles:
                 h.remove()
-        self._leader = {n: leader.get(n, n) for n in layers}
+        self._leader.update({n: state["leader"].get(n, n) for n in layers})
         return quantizers
+
+    # ------------------------------------------------------------------ block-wise calibration
+    @torch.no_grad()
+    def _capture_block_inputs(self, model: nn.Module, blocks: nn.ModuleList, batches: List,
+                              outside: Dict[str, nn.Module], outside_q: Dict[str, GPTQ],
+                              state: dict, stop_early: bool):
+        """Runs the model on every batch up to its first block and records what the block is
+        called with.  On the first batch the pass goes on to the second block, whose input is
+        kept to check the replay.  Layers outside the blocks are calibrated here when the pass
+        may not stop early."""
+        captured: List[Tuple[tuple, dict]] = []
+        probe: Dict[str, torch.Tensor] = {}
+        want_probe = {"on": True}
+
+        def first_hook(module, args, kwargs):
+            captured.append((tuple(a.detach() if torch.is_tensor(a) else a for a in args),
+                             dict(kwargs)))
+            if stop_early and not want_probe["on"]:
+                raise _StopForward()
+
+        def second_hook(module, args, kwargs):
+            if want_probe["on"]:
+                h = args[0] if args else kwargs.get("hidden_states")
+                probe["h1"] = h.detach()
+                if stop_early:
+                    raise _StopForward()
+
+        handles = [blocks[0].register_forward_pre_hook(first_hook, with_kwargs=True),
+                   blocks[1].register_forward_pre_hook(second_hook, with_kwargs=True)]
+        handles += self._hook_layers(outside, outside_q, state) if not stop_early else []
+        extra = self._forward_extras(model)
+        try:
+            for batch in batches:
+                try:
+                    self._run_model(model, batch, extra)
+                except _StopForward:
+                    pass
+                want_probe["on"] = False
+                state.setdefault("seen", []).clear()
+                state["first"] = False
+        finally:
+            for h in handles:
+                h.remove()
+        return captured, probe.get("h1")
+
+    @staticmethod
+    def _block_call(block: nn.Module, h: torch.Tensor, args: tuple, kwargs: dict) -> torch.Tensor:
+        kw = dict(kwargs)
+        if "past_key_values" in kw:
+            kw["past_key_values"] = None
+        if "use_cache" in kw:
+            kw["use_cache"] = False
+        if args:
+            out = block(h, *args[1:], **kw)
+        else:
+            kw["hidden_states"] = h
+            out = block(**kw)
+        return out[0] if isinstance(out, (tuple, list)) else out
+
+    # ------------------------------------------------------------------ exchange, chains, sharing
+    def _dispatch(self, groups: List[_Group], load: List[float]) -> None:
+        """Places the groups on ranks (greedy on the cumulative load, heaviest first), starts
+        the reduction of their Hessians and enqueues the owners' chains on the side streams."""
+        cfg, co, dc = self.quant_config, self.coordinator, self.dist_config
+        world, rank = dc.world_size, dc.rank
+        owner_mode = dc.hessian_exchange == "owner" and world > 1
+        costs = [sum(layer_cost(*q._weight_matrix().shape) for q in g.q) for g in groups]
+        order = sorted(range(len(groups)), key=lambda i: (-costs[i], i))
+        for i in order:
+            g = groups[i]
+            if owner_mode:
+                g.owner = min(range(world), key=lambda k: (load[k], k))
+                load[g.owner] += costs[i]
+            else:
+                g.owner = rank
+            g.mine = g.owner == rank
+        n_global = self._n_global
+        if world > 1:
+            for g in groups:    # same order on every rank
+                lead = g.q[0]
+                if lead._Hbuf is None:   # this rank saw no sample: it still takes part
+                    K8 = (lead.columns + 7) // 8 * 8
+                    lead._Hbuf = torch.zeros((K8, K8), dtype=torch.float32, device=co.device)
+                t0 = self._mark()
+                if owner_mode:
+                    g.reduce_work = co.comm.reduce_tensor(lead._Hbuf, dst=g.owner, async_op=True)
+                else:
+                    g.reduce_work = co.comm.all_reduce_tensor(lead._Hbuf, async_op=True)
+                lead._lower_stale = True    # the partial sums only carry the upper triangle
+                self._span("exchange_s", t0, g.reduce_work)
+        if self._pool is None:      # made once: the caching allocator pools memory per stream
+            self._pool = ChainPool(co.device, n_streams=4)
+        fmt = io.file_format(cfg.bits)
+        for i in order:             # heaviest chain first
+            g = groups[i]
+            lead = g.q[0]
+            if not g.mine:
+                lead.free_hessian()
+                continue
+            lead.nsamples = n_global
+            for q in g.q[1:]:
+                q._Hbuf, q.nsamples = lead._Hbuf, n_global
+            if self.keep_hessians:
+                if g.reduce_work is not None:
+                    g.reduce_work.wait()
+                for m in g.members:
+                    self.hessians[m] = lead.H.detach().cpu().clone()
+
+            def chain(g=g):
+                if g.reduce_work is not None:
+                    g.reduce_work.wait()        # this side stream waits, the host does not
+                status = quantize_group_launch(g.q)
+                packed = [io.packed_state(m, q, fmt) for m, q in zip(g.members, g.q)]
+                return status, packed
+
+            g.future = self._pool.submit(chain)
+
+    def _share_layout(self, groups: List[_Group], owner: int):
+        """Pieces of the flat buffer rank ``owner`` sends for one block: for every layer it
+        quantized the packed tensors, optionally the dequantized weight, then the status words
+        and error sums of its groups.  Sizes follow from shapes and settings alone, so every
+        rank lays the buffer out identically.  Returns ``(pieces, total_bytes)`` with pieces
+        ``(kind, group, member_index, key, shape, dtype, offset)``."""
+        cfg = self.quant_config
+        fmt = io.file_format(cfg.bits)
+        pieces, off = [], 0
+
+        def add(kind, g, mi, key, shape, dtype):
+            nonlocal off
+            n = 1
+            for s in shape:
+                n *= s
+            pieces.append((kind, g, mi, key, tuple(shape), dtype, off))
+            off = _align(off + n * torch.empty((), dtype=dtype).element_size())
+
+        for g in groups:
+            if g.owner != owner:
+                continue
+            for mi, (m, q) in enumerate(zip(g.members, g.q)):
+                N_out, K = q._weight_matrix().shape
+                for key, shape, dtype in io.packed_shapes(m, N_out, K, cfg.bits, cfg.group_size, fmt):
+                    add("packed", g, mi, key, shape, dtype)
+                if self.share_weights:
+                    add("weight", g, mi, "weight", tuple(q.layer.weight.shape), q.layer.weight.dtype)
+            add("info", g, -1, "info", (2,), torch.int32)
+            add("hinfo", g, -1, "hessian_info", (2,), torch.int32)
+            add("terr", g, -1, "terr", (len(g.members),), torch.float64)
+        return pieces, off
+
+    @staticmethod
+    def _piece(flat: torch.Tensor, shape, dtype, off: int) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return flat[off:off + nbytes].view(dtype).view(shape)
+
+    def _share_block(self, groups: List[_Group]) -> list:
+        """One broadcast per owning rank of everything it produced for this block.  Enqueued on
+        a stream of its own, which waits for the owner's chains; returns what `_finalize`
+        needs."""
+        co, dc = self.coordinator, self.dist_config
+        dev = co.device
+        if self._share_stream is None:
+            self._share_stream = torch.cuda.Stream(device=dev)
+        shared = []
+        main = torch.cuda.current_stream(dev)
+        for owner in sorted({g.owner for g in groups}):
+            pieces, total = self._share_layout(groups, owner)
+            mine = owner == dc.rank
+            results = {}
+            if mine:
+                for g in groups:
+                    if g.owner == owner:
+                        results[id(g)] = g.future.result()      # enqueued (not necessarily run)
+                self._pool.stream_wait(self._share_stream,
+                                       [g.future for g in groups if g.owner == owner])
+            with torch.cuda.stream(self._share_stream):
+                flat = torch.empty(max(total, 16), dtype=torch.uint8, device=dev)
+                if mine:
+                    for kind, g, mi, key, shape, dtype, off in pieces:
+                        dst = self._piece(flat, shape, dtype, off)
+                        status, packed = results[id(g)]
+                        if kind == "packed":
+                            dst.copy_(packed[mi][key].reshape(shape))
+                        elif kind == "weight":
+                            dst.copy_(g.q[mi].layer.weight.data)
+                        else:
+                            dst.copy_(status[key].reshape(shape))
+                t0 = self._mark()
+                work = co.comm.broadcast_tensor(flat, src=owner, async_op=True)
+                self._span("share_s", t0, work)
+                work.wait()
+                tail = [p for p in pieces if p[0] in ("info", "hinfo", "terr")]
+                host = {}
+                for kind, g, mi, key, shape, dtype, off in tail:
+                    h = torch.empty(shape, dtype=dtype, pin_memory=True)
+                    h.copy_(self._piece(flat, shape, dtype, off), non_blocking=True)
+                    host[(id(g), key)] = h
+                done = torch.cuda.Event()
+                done.record(self._share_stream)
+            flat.record_stream(main)
+            shared.append({"owner": owner, "flat": flat, "pieces": pieces, "host": host,
+                           "done": done})
+        return shared
+
+    # ------------------------------------------------------------------ profiling helpers
+    def _mark(self):
+        if not self.profile:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def _span(self, key: str, start, work=None) -> None:
+        """Adds (now - start) on the current stream to timings[key]; with `work`, the span is
+        measured on a stream of its own that waits for the collective."""
+        if start is None:
+            return
+        if work is not None:
+            dev = self.coordinator.device
+            s = self._probe_streams[self._probe_next % len(self._probe_streams)]
+            self._probe_next += 1
+            s.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(s):
+                a = torch.cuda.Event(enable_timing=True)
+                a.record()
+                work.wait()
+                b = torch.cuda.Event(enable_timing=True)
+                b.record()
+            self._spans.append((key, a, b))
+            return
+        b = torch.cuda.Event(enable_timing=True)
+        b.record()
+        self._spans.append((key, start, b))
+
+    # ------------------------------------------------------------------ finishing a block
+    def _finalize(self, names: List[str], layers: Dict[str, nn.Module], groups: List[_Group],
+                  shared: Optional[list]) -> Dict[str, dict]:
+        """Waits for a block's chains (and broadcasts), raises on a device-side failure - the
+        same one on every rank - and returns ``{layer: {"stats", "packed"}}``."""
+        cfg, co, dc = self.quant_config, self.coordinator, self.dist_config
+        results: Dict[str, dict] = {}
+        cur = torch.cuda.current_stream(co.device)
+        if shared is not None:
+            for sh in shared:
+                sh["done"].synchronize()
+                cur.wait_event(sh["done"])
+            for sh in shared:       # every rank sees the same status words
+                for kind, g, mi, key, shape, dtype, off in sh["pieces"]:
+                    if kind == "hinfo":
+                        _C.raise_on_info(sh["host"][(id(g), key)], f"hessian accumulation ({g.leader})")
+                    elif kind == "info":
+                        _C.raise_on_info(sh["host"][(id(g), key)], f"damped inverse ({g.leader})")
+        for g in groups:
+            if g.mine:
+                status, packed = g.future.result()
+                for mi, (m, q) in enumerate(zip(g.members, g.q)):
+                    stats = q.quantize_finish()
+                    for t in packed[mi].values():
+                        t.record_stream(cur)
+                    results[m] = {"stats": stats, "packed": packed[mi]}
+                    q.codes = None
+                    if mi > 0:
+                        q._Hbuf = None
+                g.q[0].free_hessian()
+        if shared is not None:
+            for sh in shared:
+                if sh["owner"] == dc.rank:
+                    continue
+                per_layer: Dict[Tuple[int, int], dict] = {}
+                for kind, g, mi, key, shape, dtype, off in sh["pieces"]:
+                    if kind == "packed":
+                        per_layer.setdefault((id(g), mi), {})[key] = self._piece(sh["flat"], shape, dtype, off)
+                    elif kind == "weight":
+                        g.q[mi].layer.weight.data = self._piece(sh["flat"], shape, dtype, off)
+                for g in groups:
+                    if g.owner != sh["owner"]:
+                        continue
+                    terr = sh["host"][(id(g), "terr")]
+                    for mi, (m, q) in enumerate(zip(g.members, g.q)):
+                        packed = per_layer[(id(g), mi)]
+                        bias = getattr(q.layer, "bias", None)
+                        if bias is not None:     # not quantized: the local copy
+                            packed[f"{m}.bias"] = bias.data
+                        per_channel = cfg.group_size <= 0 or cfg.group_size >= q.columns
+                        ng = 1 if per_channel else -(-q.columns // cfg.group_size)
+                        N_out = q._weight_matrix().shape[0]
+                        results[m] = {"packed": packed, "stats": {
+                            "bits": cfg.bits, "group_size": cfg.group_size,
+                            "total_error": float(terr[mi].item()),
+                            "compression_ratio": 32.0 / cfg.bits,
+                            "scale_shape": torch.Size((N_out, ng)),
+                            "zero_shape": torch.Size((N_out, ng))}}
+        return results
+
+    def _record(self, name: str, layer: nn.Module, entry: dict) -> None:
+        cfg = self.quant_config
+        self.quantized_layers[name] = entry["stats"]
+        self.quantization_errors[name] = entry["stats"].get("total_error", 0)
+        self.packed[name] = entry["packed"]
+        W = layer.weight.data.flatten(1) if layer.weight.dim() > 2 else layer.weight.data
+        self.layer_info[name] = {
+            "bits": cfg.bits, "group_size": cfg.group_size,
+            "out_features": W.shape[0], "in_features": W.shape[1],
+            "kind": "conv2d" if isinstance(layer, nn.Conv2d) else "linear",
+            "weight_shape": list(layer.weight.shape),
+            "packing": "int32_le" if io.file_format(cfg.bits) == _C.FMT_INT32_LE else "bytes_lo_first"}
+
+    def _groups_of(self, names: List[str], quantizers: Dict[str, GPTQ]) -> List[_Group]:
+        by_leader: Dict[str, List[str]] = {}
+        for n in names:
+            by_leader.setdefault(self._leader[n], []).append(n)
+        groups = []
+        for lead, members in by_leader.items():
+            members = [lead] + [m for m in members if m != lead]
+            # layers of one group are stacked into one matrix: same width required
+            K = quantizers[lead].columns
+            same = [m for m in members if quantizers[m].columns == K]
+            groups.append(_Group(lead, same, quantizers))
+            for m in members:
+                if m not in same:       # cannot happen for layers fed the same tensor
+                    raise RuntimeError(f"{m} shares an input with {lead} but not its width")
+        return groups
+
+    def _check_grouping(self, names: List[str]) -> None:
+        """All ranks must have found the same grouping: it decides order and size of every
+        collective that follows."""
+        co = self.coordinator
+        if not co.comm.active:
+            return
+        mine = [(n, self._leader[n]) for n in names]
+        ref = co.comm.broadcast_object(mine, src=0)
+        if ref != mine:
+            raise RuntimeError("ranks disagree on which layers share an input; "
+                               "the calibration passes took different paths through the model")
 
     # ------------------------------------------------------------------ main entry
     def quantize_model(self, model: nn.Module,
@@ -204,113 +653,34 @@ class DistributedGPTQuantizer:
             samples = calibration_samples(calibration_data, cfg.calibration_samples)
             if not samples:
                 raise ValueError("no calibration data")
-            n_global = len(samples)
+            self._n_global = len(samples)
+            self._leader = {}
+            first_sample = samples[0]
             samples = co.shard_calibration(samples)
+            batches = make_batches(samples, self.calibration_batch_size)
+            self.timings = {}
+            self._spans = []
+            self._probe_next = 0
+            self._probe_streams = ([torch.cuda.Stream(device=co.device) for _ in range(8)]
+                                   if self.profile else [])
+            self._progress = {"done": 0, "total": len(layers), "cb": progress_callback}
+            self._results: Dict[str, dict] = {}
 
-            t0 = time.time()
-            quantizers = self._accumulate_hessians(model, samples, layers)
+            plan = find_blocks(model, layers) if self.blockwise else None
+            done = False
+            if plan is not None:
+                done = self._quantize_blockwise(model, plan, layers, batches, first_sample)
+            if not done:
+                self._quantize_whole(model, layers, batches, first_sample)
             torch.cuda.synchronize(co.device)
-            self.timings["calibration_s"] = time.time() - t0
 
-            # ---- exchange: partial Hessians -> owners
-            t0 = time.time()
-            names = list(layers)
-            groups: Dict[str, List[str]] = {}
-            for n in names:
-                groups.setdefault(self._leader[n], []).append(n)
-            leaders = list(groups)
-            costs = [sum(layer_cost(*quantizers[m]._weight_matrix().shape) for m in groups[g])
-                     for g in leaders]
-            world = self.dist_config.world_size
-            owners_list = assign_owners(costs, world) if self.dist_config.hessian_exchange == "owner" \
-                else [self.dist_config.rank] * len(leaders)
-            owner_of_group = dict(zip(leaders, owners_list))
-            if world > 1:
-                for g in leaders:   # a rank whose shard was empty still needs a buffer to reduce
-                    q = quantizers[g]
-                    if q._Hbuf is None:
-                        K8 = (q.columns + 7) // 8 * 8
-                        q._Hbuf = torch.zeros((K8, K8), dtype=torch.float32, device=co.device)
-                co.exchange_hessians({g: quantizers[g]._Hbuf for g in leaders}, owner_of_group)
-            for g in leaders:
-                quantizers[g].nsamples = n_global
-            self.timings["exchange_s"] = time.time() - t0
-
-            # ---- quantize the layers this rank owns
-            t0 = time.time()
-            all_reduce_mode = self.dist_config.hessian_exchange != "owner" or world == 1
-            results: Dict[str, dict] = {}
-            # The layers of a stage are independent once their Hessians are complete: their
-            # chains (damped inverse, block quantization, packing) are enqueued on side
-            # streams, where they run beside each other, and collected afterwards.
-            if self._pool is None:      # made once: the caching allocator pools memory per stream
-                self._pool = ChainPool(co.device, n_streams=4)
-            pool = self._pool
-            launched = []
-            for g in leaders:
-                mine = all_reduce_mode or owner_of_group[g] == self.dist_config.rank
-                if mine:
-                    for n in groups[g]:
-                        q = quantizers[n]
-                        if n != g:
-                            q._Hbuf, q.nsamples = quantizers[g]._Hbuf, n_global
-                        if self.keep_hessians:
-                            self.hessians[n] = q.H.detach().cpu().clone()
-
-                        def chain(n=n, q=q):
-                            q.quantize_launch()
-                            return io.packed_state(n, q, io.file_format(cfg.bits))
-
-                        launched.append((n, g, q, pool.submit(chain)))
-            for n, g, q, fut in launched:
-                packed = fut.result()
-                stats = q.quantize_finish()
-                for t in packed.values():
-                    t.record_stream(torch.cuda.current_stream(co.device))
-                results[n] = {"stats": stats, "packed": packed}
-                q.codes = None
-                if n != g:
-                    q._Hbuf = None
-            pool.join()
-            for g in leaders:
-                quantizers[g].free_hessian()
-            torch.cuda.synchronize(co.device)
-            self.timings["quantize_s"] = time.time() - t0
-
-            # ---- share results: every rank ends with the same quantized model
-            t0 = time.time()
-            for idx, n in enumerate(names):
-                g = self._leader[n]
-                layer = layers[n]
-                if not all_reduce_mode:
-                    src = owner_of_group[g]
-                    entry = results.get(n)
-                    shapes = co.comm.broadcast_object(
-                        {k: (tuple(v.shape), v.dtype) for k, v in entry["packed"].items()}
-                        if entry else None, src=src)
-                    stats = co.comm.broadcast_object(entry["stats"] if entry else None, src=src)
-                    if entry is None:
-                        entry = {"stats": stats, "packed": {
-                            k: (layer.bias.data if k.endswith(".bias")      # not quantized: local copy
-                                else torch.empty(s, dtype=d, device=co.device))
-                            for k, (s, d) in shapes.items()}}
-                        results[n] = entry
-                    for k in sorted(entry["packed"]):
-                        if not k.endswith(".bias"):
-                            co.comm.broadcast_tensor(entry["packed"][k], src=src)
-                    co.comm.broadcast_tensor(layer.weight.data, src=src)
-                entry = results[n]
-                self.quantized_layers[n] = entry["stats"]
-                self.quantization_errors[n] = entry["stats"].get("total_error", 0)
-                self.packed[n] = entry["packed"]
-                W = layer.weight.data.flatten(1) if layer.weight.dim() > 2 else layer.weight.data
-                self.layer_info[n] = {"bits": cfg.bits, "group_size": cfg.group_size,
-                                      "out_features": W.shape[0], "in_features": W.shape[1],
-                                      "packing": "int32_le" if io.file_format(cfg.bits) == _C.FMT_INT32_LE
-                                      else "bytes_lo_first"}
-                if progress_callback and self.dist_config.rank == 0:
-                    progress_callback(idx + 1, len(names), n, entry["stats"])
-            self.timings["share_s"] = time.time() - t0
+            for n in layers:        # model order
+                self._record(n, layers[n], self._results[n])
+            self._results = {}
+            if self.profile:
+                for key, a, b in self._spans:
+                    self.timings[key] = self.timings.get(key, 0.0) + a.elapsed_time(b) * 1e-3
+            self._spans = []
             self.timings["total_s"] = time.time() - start
             if self.dist_config.rank == 0:
                 self._log_quantization_summary(time.time() - start)
@@ -318,9 +688,169 @@ class DistributedGPTQuantizer:
                 self.save_quantized_model(model, save_path)
         return model
 
+    def _report(self, names: List[str], results: Dict[str, dict]) -> None:
+        self._results.update(results)
+        p = self._progress
+        for n in names:
+            p["done"] += 1
+            if p["cb"] and self.dist_config.rank == 0:
+                p["cb"](p["done"], p["total"], n, results[n]["stats"])
+
+    # ---- one pass over the whole model per batch, then all layers
+    def _quantize_whole(self, model, layers, batches, first_sample) -> None:
+        co, dc = self.coordinator, self.dist_config
+        self.mode_used = "whole-model"
+        t0 = time.time()
+        quantizers = self._accumulate_hessians(model, batches, layers, discovery_batch=first_sample)
+        names = list(layers)
+        self._check_grouping(names)
+        self.timings["calibration_s"] = time.time() - t0
+        groups = self._groups_of(names, quantizers)
+        load = [0.0] * dc.world_size
+        self._dispatch(groups, load)
+        owner_mode = dc.hessian_exchange == "owner" and dc.world_size > 1
+        shared = self._share_block(groups) if owner_mode else None
+        self._report(names, self._finalize(names, layers, groups, shared))
+        self._pool.join()
+
+    # ---- block by block
+    @torch.no_grad()
+    def _quantize_blockwise(self, model, plan, layers, batches, first_sample) -> bool:
+        cfg, co, dc = self.quant_config, self.coordinator, self.dist_config
+        list_name, blocks = plan
+        prefix = list_name + "." if list_name else ""
+        per_block: List[Dict[str, nn.Module]] = [dict() for _ in blocks]
+        outside: Dict[str, nn.Module] = {}
+        for n, layer in layers.items():
+            head = n[len(prefix):].split(".", 1)[0] if n.startswith(prefix) else ""
+            if head.isdigit() and int(head) < len(blocks):
+                per_block[int(head)][n] = layer
+            else:
+                outside[n] = layer
+        owner_mode = dc.hessian_exchange == "owner" and dc.world_size > 1
+        load = [0.0] * dc.world_size
+        sequential = cfg.true_sequential
+        ckpt = Path(cfg.checkpoint_dir) if cfg.checkpoint_dir else None
+
+        # ---- inputs of the first block (and, in one-shot mode, the layers outside the blocks:
+        # they see the activations of the unquantized model, so their pass comes first)
+        state = {"first": True}
+        outside_q = self._new_quantizers(outside)
+        run_batches = batches if batches else make_batches([first_sample], 1)
+        discovery_only = not batches
+        state["accumulate"] = not discovery_only
+        outside_now = bool(outside) and not sequential
+        t_cal = self._mark()
+        captured, h1 = self._capture_block_inputs(model, blocks, run_batches, outside, outside_q,
+                                                  state, stop_early=not outside_now)
+        if not captured or len(captured) != len(run_batches):
+            logger.warning("block-wise calibration: %s[0] was not reached once per batch; "
+                           "using whole-model passes", list_name)
+            return False
+        hidden = [(c[0][0] if c[0] else c[1]["hidden_states"]) for c in captured]
+        # replay check: the first block, called as recorded, must reproduce the second block's input
+        if h1 is not None:
+            out = self._block_call(blocks[0], hidden[0], captured[0][0], captured[0][1])
+            ok = out.shape == h1.shape and torch.allclose(out.float(), h1.float(), rtol=1e-3, atol=1e-5)
+            del out
+            if not ok:
+                logger.warning("block-wise calibration: replaying %s[0] does not reproduce the "
+                               "input of %s[1]; using whole-model passes", list_name, list_name)
+                return False
+        self.mode_used = "block-wise" + (" true-sequential" if sequential else "")
+        self._span("forward_s", t_cal)
+        if outside_now:
+            self._leader.update({n: state["leader"].get(n, n) for n in outside})
+            self._check_grouping(list(outside))
+            og = self._groups_of(list(outside), outside_q)
+            self._dispatch(og, load)
+            pending_outside = (list(outside), og, self._share_block(og) if owner_mode else None)
+        else:
+            pending_outside = None
+
+        lag: List[tuple] = []       # blocks whose chains are enqueued but not collected yet
+        for b, block in enumerate(blocks):
+            targets = per_block[b]
+            names_b = list(targets)
+            shard = ckpt / f"block_{b:05d}.safetensors" if ckpt is not None else None
+            resumed = None
+            if shard is not None and targets and shard.is_file():
+                resumed = io.load_block_shard(shard, targets, cfg, co.device)
+                if sequential:      # later blocks are calibrated on the quantized model
+                    io.apply_block_weights(targets, resumed)
+            quantizers = self._new_quantizers(targets) if resumed is None else {}
+            bstate = {"first": True, "accumulate": not discovery_only}
+            handles = self._hook_layers(targets, quantizers, bstate) if resumed is None else []
+            nxt = []
+            t0 = self._mark()
+            try:
+                for i, h in enumerate(hidden):
+                    out = self._block_call(block, h, captured[i][0], captured[i][1])
+                    bstate.setdefault("seen", []).clear()
+                    bstate["first"] = False
+                    if not sequential or resumed is not None or not targets:
+                        nxt.append(out)
+            finally:
+                for hd in handles:
+                    hd.remove()
+            self._span("forward_s", t0)
+            if resumed is not None:
+                if not sequential:  # one-shot: every block sees the unquantized model's activations
+                    io.apply_block_weights(targets, resumed)
+                for n in names_b:
+                    self._leader[n] = resumed["leader"].get(n, n)
+                self._report(names_b, resumed["results"])
+                hidden = nxt
+                continue
+            if targets:
+                self._leader.update({n: bstate["leader"].get(n, n) for n in names_b})
+                if b == 0:
+                    self._check_grouping(names_b)
+                groups = self._groups_of(names_b, quantizers)
+                self._dispatch(groups, load)
+                shared = self._share_block(groups) if owner_mode else None
+                lag.append((b, names_b, targets, groups, shared, shard))
+            if sequential and targets:
+                # the next block must see this block's quantized weights: collect now, re-run
+                self._collect(lag.pop())
+                t0 = self._mark()
+                nxt = [self._block_call(block, h, captured[i][0], captured[i][1])
+                       for i, h in enumerate(hidden)]
+                self._span("forward_s", t0)
+            elif len(lag) > 2:
+                self._collect(lag.pop(0))    # bounds how far the host runs ahead of the device
+            hidden = nxt
+        while lag:
+            self._collect(lag.pop(0))
+        if pending_outside is not None:
+            names_o, og, sh = pending_outside
+            self._report(names_o, self._finalize(names_o, outside, og, sh))
+        elif outside:
+            # true-sequential: the layers after the blocks see the quantized model
+            oq = self._accumulate_hessians(model, batches, outside, discovery_batch=first_sample)
+            names_o = list(outside)
+            self._check_grouping(names_o)
+            og = self._groups_of(names_o, oq)
+            self._dispatch(og, load)
+            sh = self._share_block(og) if owner_mode else None
+            self._report(names_o, self._finalize(names_o, outside, og, sh))
+        if self._pool is not None:
+            self._pool.join()
+        return True
+
+    def _collect(self, item) -> None:
+        b, names_b, targets, groups, shared, shard = item
+        results = self._finalize(names_b, targets, groups, shared)
+        if shard is not None and self.dist_config.rank == 0:
+            io.save_block_shard(shard, names_b, targets, results,
+                                {n: self._leader[n] for n in names_b}, self.quant_config)
+        self._report(names_b, results)
+
     # ------------------------------------------------------------------ save / load
     def _metadata(self) -> dict:
-        return {"quantization_config": asdict(self.quant_config),
+        config = asdict(self.quant_config)
+        config.pop("checkpoint_dir", None)     # where shards were kept is not a property of the result
+        return {"quantization_config": config,
                 "quantized_layers": list(self.quantized_layers.keys()),
                 "quantization_errors": self.quantization_errors,
                 "layers": self.layer_info}
@@ -367,9 +897,9 @@ class DistributedGPTQuantizer:
     def _log_quantization_summary(self, elapsed: float) -> None:
         n = len(self.quantization_errors)
         avg = sum(self.quantization_errors.values()) / n if n else 0.0
-        logger.info("Quantized %d layers to %d bits (group %d) in %.2f s; average error %.6f; "
+        logger.info("Quantized %d layers to %d bits (group %d) in %.2f s (%s); average error %.6f; "
                     "peak GPU memory %.2f GB", n, self.quant_config.bits,
-                    self.quant_config.group_size, elapsed, avg,
+                    self.quant_config.group_size, elapsed, self.mode_used, avg,
                     self.coordinator.get_memory_stats()["max_allocated_gb"])
 
 

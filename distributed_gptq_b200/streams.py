@@ -77,10 +77,23 @@ class ChainPool:
             fut = self._workers[i].submit(run)
         self._jobs.append(fut)
         out_fut: Future = Future()
-        fut.add_done_callback(
-            lambda f: out_fut.set_exception(f.exception()) if f.exception() is not None
-            else out_fut.set_result(f.result()[0]))
+
+        def deliver(f):
+            if f.exception() is not None:
+                out_fut.set_exception(f.exception())
+            else:
+                out_fut.done_event = f.result()[1]     # recorded on the side stream after fn
+                out_fut.set_result(f.result()[0])
+
+        fut.add_done_callback(deliver)
         return out_fut
+
+    def stream_wait(self, stream: torch.cuda.Stream, futures: Iterable[Future]) -> None:
+        """Makes ``stream`` wait for the chains behind ``futures`` (as returned by
+        :meth:`submit`); blocks the host only until those chains are enqueued."""
+        for f in futures:
+            f.result()
+            stream.wait_event(f.done_event)
 
     def join(self) -> None:
         cur = torch.cuda.current_stream(self.device)

@@ -77,6 +77,18 @@ int32_t dgq_hessian_accum(const void* X_bf16, int64_t T, int32_t K, int64_t ldx,
                           float* H, int64_t ldh, float alpha, int32_t splits,
                           int32_t* info, void* stream);
 
+/* The same accumulation restricted to the part of H on and above the diagonal; what lies
+ * below the diagonal is neither read nor written.  X^T X is symmetric, so a caller that
+ * accumulates many batches (core/gptq.py:63-89 is called once per calibration batch) can
+ * skip the mirrored half of every update - half of the kernel's reduction traffic - and call
+ * dgq_hessian_mirror once, before the matrix is read as a whole (core/gptq.py:112-122).
+ */
+int32_t dgq_hessian_accum_upper(const void* X_bf16, int64_t T, int32_t K, int64_t ldx,
+                                float* H, int64_t ldh, float alpha, int32_t splits,
+                                int32_t* info, void* stream);
+/* H[i][j] = H[j][i] for i > j. */
+int32_t dgq_hessian_mirror(float* H, int32_t K, int64_t ldh, void* stream);
+
 /* fp32 -> bf16 (round to nearest even) for activations that arrive as fp32
  * (core/gptq.py:88 upcasts; the tensor-core path takes bf16). n elements. */
 int32_t dgq_cast_f32_to_bf16(const float* src, void* dst_bf16, int64_t n, void* stream);
@@ -164,6 +176,19 @@ int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int64_t ldu,
                           int32_t blocksize, uint8_t* codes, int64_t ldc,
                           float* scales, float* zeros, double* total_error,
                           void* ws, int64_t ws_bytes, void* stream);
+
+/* dgq_gptq_quantize with one more output: row_error (N_out doubles, may be null) receives
+ * sum(((w - w_hat)/d)^2) of every weight row, the per-row split of total_error
+ * (core/gptq.py:183,191).  Rows are independent given U, so layers that read the same
+ * input (one Hessian, one U: q/k/v or gate/up of a decoder block) can be quantized as one
+ * stacked matrix; the per-layer `total_error` of the reference's stats (core/gptq.py:203-210)
+ * is then the sum of the layer's rows.
+ */
+int32_t dgq_gptq_quantize_rows(float* W, int64_t ldw, const float* U, int64_t ldu,
+                               int32_t N_out, int32_t K, int32_t bits, int32_t group_size,
+                               int32_t blocksize, uint8_t* codes, int64_t ldc,
+                               float* scales, float* zeros, double* total_error,
+                               double* row_error, void* ws, int64_t ws_bytes, void* stream);
 
 /* Same computation as dgq_gptq_quantize for callers that must not allocate device
  * memory - code running inside another framework's memory plan, or under an allocator

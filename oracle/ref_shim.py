@@ -12,7 +12,10 @@ import importlib.util
 import os
 import sys
 
-DEFAULT_ROOT = os.environ.get("DGQ_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: named by DGQ_REFERENCE_ROOT, else a directory `reference` beside this
+# repository; absent on machines that only run the GPU tests (callers check `available()`)
+DEFAULT_ROOT = os.environ.get("DGQ_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 _SUB = "src/distributed_gptq"
 
 

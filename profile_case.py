@@ -1,11 +1,11 @@
 """Runs one kernel of the library a few times on a small seeded case, for profilers.
 
-    python -m distributed_gptq_b200.profile_case hessian   --K 4096 --T 32768
-    python -m distributed_gptq_b200.profile_case inv_chol  --K 4096
-    python -m distributed_gptq_b200.profile_case quantize  --K 4096 --N 4096
-    python -m distributed_gptq_b200.profile_case pack      --K 8192 --N 16384
-    python -m distributed_gptq_b200.profile_case dequant   --K 8192 --N 16384
-    python -m distributed_gptq_b200.profile_case qlinear   --K 5120 --N 5120 --M 16
+    python profile_case.py hessian   --K 4096 --T 32768
+    python profile_case.py inv_chol  --K 4096
+    python profile_case.py quantize  --K 4096 --N 4096
+    python profile_case.py pack      --K 8192 --N 16384
+    python profile_case.py dequant   --K 8192 --N 16384
+    python profile_case.py qlinear   --K 5120 --N 5120 --M 16
 
 Prints the CUDA-event time of each repetition and the derived rate (algorithmic flops
 or bytes over time).  Sizes default to a few hundred MB so that a profiler capture ends
@@ -14,10 +14,13 @@ quickly while the inputs still exceed the L2 cache.
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
 import torch
 
-from . import _C
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from distributed_gptq_b200 import _C  # noqa: E402
 
 
 def _time(fn, reps):

@@ -100,6 +100,25 @@ def _worker(rank, world, port, mode, q):
             assert co.comm.broadcast_object({"x": rank}, src=0) == {"x": 0}
             shard = co.shard_calibration(list(range(7)))
             assert shard == list(range(rank, 7, world))
+            # the reference's name for the split (coordinator.py:147-181): lists and DataLoaders
+            assert co.distribute_calibration_data(list(range(7))) == shard
+            from torch.utils.data import DataLoader, TensorDataset
+            dl = DataLoader(TensorDataset(torch.arange(10).float()), batch_size=2)
+            mine = torch.cat([b[0] for b in co.distribute_calibration_data(dl)])
+            assert mine.tolist() == [float(i) for i in range(rank, 10, world)]
+            # every rank must have found the same grouping of layers; one that did not is told
+            from distributed_gptq_b200 import DistributedGPTQuantizer
+            qz = DistributedGPTQuantizer.__new__(DistributedGPTQuantizer)
+            qz.coordinator = co
+            qz._leader = {"a": "a", "b": "a"}
+            qz._check_grouping(["a", "b"])
+            qz._leader = {"a": "a", "b": "a" if rank == 0 else "b"}
+            try:
+                qz._check_grouping(["a", "b"])
+                disagreed = False
+            except RuntimeError as e:
+                disagreed = "disagree" in str(e)
+            assert disagreed == (rank == 1)
             co.comm.barrier()
         assert not dist.is_initialized()
         q.put((rank, "ok"))
@@ -119,3 +138,86 @@ def test_exchange_over_gloo(mode):
     for p in procs:
         p.join(timeout=60)
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_reference_method_names_exist():
+    """Callers written against the reference's coordinator find its methods
+    (reference coordinator.py:147-235)."""
+    from distributed_gptq_b200.coordinator import DistributedConfig, DistributedGPTQCoordinator
+    co = DistributedGPTQCoordinator(DistributedConfig())
+    assert callable(co.quantize_layer_distributed) and callable(co.distribute_calibration_data)
+    data = [1, 2, 3]
+    assert co.distribute_calibration_data(data) is data     # single process: unchanged
+
+
+def test_device_status_words_raise():
+    """The host half of the device status path: the two words a kernel leaves behind become
+    Python errors that name the condition."""
+    import pytest
+    from distributed_gptq_b200 import _C
+    _C.raise_on_info(torch.tensor([_C.INFO_OK, 0], dtype=torch.int32), "x")
+    with pytest.raises(RuntimeError, match=r"inverse.*not positive definite \(pivot 17\)"):
+        _C.raise_on_info(torch.tensor([_C.INFO_NOT_POSDEF, 17], dtype=torch.int32), "damped inverse")
+    with pytest.raises(RuntimeError, match=r"bounded wait.*ran out \(wait 3\)"):
+        _C.raise_on_info(torch.tensor([_C.INFO_WAIT_TIMEOUT, 3], dtype=torch.int32), "hessian")
+    with pytest.raises(RuntimeError, match="unknown device status 9"):
+        _C.raise_on_info(torch.tensor([9, 0], dtype=torch.int32), "x")
+
+
+def test_block_discovery_and_batching():
+    import torch.nn as nn
+    from distributed_gptq_b200.quantizer import calibration_samples, find_blocks, make_batches
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.pre = nn.Linear(8, 8)
+            self.short = nn.ModuleList([nn.Linear(8, 8)])
+            self.layers = nn.ModuleList(nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 8)) for _ in range(3))
+            self.head = nn.Linear(8, 8)
+    m = M()
+    layers = {n: mod for n, mod in m.named_modules() if isinstance(mod, nn.Linear)}
+    name, blocks = find_blocks(m, layers)
+    assert name == "layers" and len(blocks) == 3
+    assert find_blocks(nn.Sequential(nn.Linear(4, 4), nn.Linear(4, 4)),
+                       {"0": None, "1": None}) is None
+    samples = calibration_samples([torch.zeros(3, 5), torch.zeros(2, 7), torch.zeros(4, 5)], 8)
+    assert len(samples) == 8
+    batches = make_batches(samples, 2)
+    assert [tuple(b.shape) for b in batches] == [(2, 5), (1, 5), (2, 7), (2, 5), (1, 5)]
+
+
+def test_share_layout_is_aligned_and_deterministic():
+    """Every rank lays the per-block result buffer out from shapes and settings alone."""
+    import torch.nn as nn
+    from distributed_gptq_b200 import DistributedGPTQuantizer, QuantizationConfig
+    from distributed_gptq_b200.coordinator import DistributedConfig
+    from distributed_gptq_b200.quantizer import _Group
+
+    class FakeQ:
+        def __init__(self, layer):
+            self.layer = layer
+            self.columns = layer.weight.shape[1]
+
+        def _weight_matrix(self):
+            return self.layer.weight.data
+    for bits, group in ((4, 128), (3, 128), (8, -1), (2, 64)):
+        qz = DistributedGPTQuantizer(QuantizationConfig(bits=bits, group_size=group), DistributedConfig())
+        lins = {"a": nn.Linear(384, 100, bias=False), "b": nn.Linear(384, 36), "c": nn.Linear(256, 50)}
+        qs = {n: FakeQ(l) for n, l in lins.items()}
+        g1, g2 = _Group("a", ["a", "b"], qs), _Group("c", ["c"], qs)
+        g1.owner, g2.owner = 1, 0
+        pieces, total = qz._share_layout([g1, g2], 1)
+        assert [p[3] for p in pieces if p[0] == "packed"][:4] == ["a.qweight", "a.scales", "a.zeros", "a.g_idx"]
+        assert all(p[6] % 16 == 0 for p in pieces) and total % 16 == 0
+        assert {p[1] for p in pieces} == {g1}
+        assert [p[0] for p in pieces][-3:] == ["info", "hinfo", "terr"] and pieces[-1][4] == (2,)
+        flat = torch.zeros(total, dtype=torch.uint8)
+        for kind, g, mi, key, shape, dtype, off in pieces:
+            view = qz._piece(flat, shape, dtype, off)
+            assert tuple(view.shape) == tuple(shape) and view.dtype == dtype
+        # non-overlapping
+        spans = sorted((p[6], p[6] + qz._piece(flat, p[4], p[5], p[6]).numel() *
+                        qz._piece(flat, p[4], p[5], p[6]).element_size()) for p in pieces)
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+        assert qz._share_layout([g1, g2], 1) == (pieces, total)

@@ -145,3 +145,79 @@ def test_fasterquant_alias_and_quantizer(dgq):
     qo = torch.clamp(torch.round(W / so[:, None] + zo[:, None]), 0, 15)
     assert torch.equal(wh, (qo - zo[:, None]) * so[:, None])
     assert torch.equal(qz.codes.cpu().float(), qo)
+
+
+# ---- the two block kernels against each other ----------------------------------------------
+def test_fast_block_kernel_against_general_kernel(dgq):
+    """Full 128-column blocks with aligned rows take gptq_block8_kernel, whose error feedback is
+    a fused multiply-add; every other layout takes gptq_block_kernel, which multiplies and
+    subtracts like the oracle.  The same matrix through both (the second time with a row pitch
+    that is not a multiple of four floats) must agree to the tolerance of the oracle
+    comparison, and each must meet the oracle's bar by itself."""
+    W, X = synth_layer(256, 1024, 4096, 21)
+    H = X.t() @ X
+    ref = O.gptq_quantize(W, H, 4, 4, 128, 128, 0.01, False)
+    Hp, _ = dgq.hessian_prepare(H.cuda(), 2.0 / 4, 0.01, None)
+    U = dgq.inv_chol_upper(Hp)
+    Wf = W.cuda().clone()
+    pitched = torch.zeros((256, 1025), device="cuda")
+    pitched[:, :1024] = W.cuda()
+    Wg = pitched[:, :1024]
+    assert Wg.stride(0) % 4 != 0
+    cf, sf, zf, ef = dgq.gptq_quantize(Wf, U, 4, 128, 128)
+    cg, sg, zg, eg = dgq.gptq_quantize(Wg, U, 4, 128, 128)
+    for c in (cf, cg):
+        d = (c.cpu().int() - ref["codes"].int()).abs()
+        assert float((d == 0).float().mean()) >= CODE_MATCH and int(d.max()) <= 1
+    d = (cf.int() - cg.int()).abs()
+    assert float((d == 0).float().mean()) >= 0.999 and int(d.max()) <= 1
+    assert abs(float(ef) - float(eg)) <= 1e-3 * float(eg)
+    assert torch.allclose(sf, sg, rtol=1e-4, atol=0)
+
+
+# ---- groups wider than a block and the width of the deferred-update window ------------------
+@pytest.mark.parametrize("K,g,ws_cols", [
+    (1536, 256, 384),     # a caller-sized workspace of 384 columns: groups would straddle it
+    (1536, 384, None),    # default workspace (512 columns), group 384
+    (2048, 1024, None),   # a group wider than the window
+    (1280, 640, None),
+])
+def test_wide_groups_see_all_earlier_updates(dgq, K, g, ws_cols):
+    """A group wider than a block takes its scale/zero from all of its columns when its first
+    column is reached; every one of them must have received the updates of all earlier blocks
+    by then (core/gptq.py:158-169 reads the outer matrix), whatever the width of the window in
+    which the library defers the updates of far columns."""
+    N_out = 160
+    W, X = synth_layer(N_out, K, 4 * K, K + g)
+    H = X.t() @ X
+    ref = O.gptq_quantize(W, H, 4, 4, g, 128, 0.01, False)
+    Hp, _ = dgq.hessian_prepare(H.cuda(), 2.0 / 4, 0.01, None)
+    U = dgq.inv_chol_upper(Hp)
+    Wd = W.cuda().clone()
+    ws = None if ws_cols is None else N_out * ws_cols * 4
+    codes, s, z, terr = dgq.gptq_quantize(Wd, U, 4, g, 128, ws_bytes=ws)
+    d = (codes.cpu().int() - ref["codes"].int()).abs()
+    assert float((d == 0).float().mean()) >= CODE_MATCH and int(d.max()) <= 1
+    assert torch.allclose(s.cpu(), ref["scale"], rtol=1e-3, atol=0)
+    assert abs(float(terr) - ref["total_error"]) <= 0.02 * ref["total_error"]
+
+
+def test_actorder_rank_with_non_finite_diagonal(dgq):
+    """The act-order ranks are a permutation for every diagonal: NaN sorts like +inf, ties go
+    to the lower index (the rule of a stable descending sort)."""
+    K = 300
+    g = torch.Generator().manual_seed(0)
+    d = torch.rand(K, generator=g) + 0.1
+    d[7] = float("nan")
+    d[100] = float("inf")
+    d[200] = float("nan")
+    d[50] = d[51] = 0.75
+    d[60] = 0.0                     # a dead column is ranked as 1.0
+    H = torch.diag(d).cuda()
+    perm, inv = dgq.actorder_perm(H, 1.0)
+    key = torch.where(torch.isnan(d), torch.full_like(d, float("inf")), d)
+    key = torch.where(key == 0, torch.ones_like(key), key)
+    want = torch.argsort(key, descending=True, stable=True)
+    assert torch.equal(perm.cpu().long(), want)
+    assert torch.equal(torch.sort(perm.cpu()).values.long(), torch.arange(K))
+    assert torch.equal(inv.cpu().long()[want], torch.arange(K))
