@@ -276,6 +276,46 @@ class ModelWorkload:
                 f"lm_head left in float")
 
 
+def linear_check(spec, device, actorder: bool):
+    """The packed 4-bit quantized linear (``torch.ops.gptq.linear``, the operator the reference's
+    ``QuantizedLinear.forward`` calls) at batch 1, 4 and 16 on the three layer shapes of the
+    model, checked against dequantize + matmul (the reference's own fallback branch,
+    models/layers.py:155-157) and timed with CUDA events over back-to-back calls."""
+    import distributed_gptq_b200  # noqa: F401
+    from distributed_gptq_b200 import _C
+    d, f, g = spec["d"], spec["ffn"], 128
+    out = []
+    gen = torch.Generator(device=device).manual_seed(7)
+    for N_out, K in ((d, d), (f, d), (d, f)):
+        codes = torch.randint(0, 16, (N_out, K), generator=gen, device=device, dtype=torch.uint8)
+        qw = _C.pack(codes, 4, _C.FMT_BYTES_LO_FIRST)
+        scales = (torch.rand(N_out, K // g, generator=gen, device=device) * 0.02 + 0.001).half()
+        zeros = torch.randint(0, 16, (N_out, K // g), generator=gen, device=device).half()
+        g_idx = (torch.arange(K, device=device) // g).to(torch.int32)
+        if actorder:
+            g_idx = g_idx[torch.randperm(K, generator=gen, device=device)]
+        W = _C.unpack_dequant(qw, scales, zeros, g_idx, K, 4, g, _C.FMT_BYTES_LO_FIRST, torch.float32)
+        for M in (1, 4, 16):
+            x = torch.randn(M, K, generator=gen, device=device).to(torch.bfloat16)
+            y = torch.ops.gptq.linear(x, qw, scales, zeros, g_idx, None)
+            want = x.double() @ W.double().t()
+            err = float((y.double() - want).abs().max() / want.abs().max())
+            reps = 200
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                torch.ops.gptq.linear(x, qw, scales, zeros, g_idx, None)
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / reps
+            nbytes = N_out * K / 2 + 4 * N_out * (K // g) + 2 * M * (K + N_out)
+            out.append({"N_out": N_out, "K": K, "M": M, "act_order": actorder, "us_per_call": round(us, 2),
+                        "algorithmic_GBs": round(nbytes / us / 1e3, 1),
+                        "max_err_vs_dequant_matmul": err, "ok": err <= 4.5e-3})
+    return out
+
+
 # ============================================================================= layer sweep
 LAYERS = [("4096x4096", 4096, 4096), ("11008x4096", 11008, 4096), ("4096x11008", 4096, 11008)]
 SETTINGS = [(4, False), (4, True), (3, False), (3, True)]   # (bits, act-order)
@@ -622,6 +662,9 @@ def main():
     ap.add_argument("--true-sequential", action="store_true")
     ap.add_argument("--cpu-outright", action="store_true",
                     help="reference arm: time the whole workload on the CPU (small models only)")
+    ap.add_argument("--linear-check", action="store_true",
+                    help="model workloads: also run the packed 4-bit linear at batch 1/4/16 on the "
+                         "model's layer shapes against dequantize + matmul")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-input pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -809,7 +852,8 @@ def main():
                     "exchange_reduce": per.get("exchange_s", 0.0),
                     "prepare_permute": round(lib.get("prepare", 0.0) + lib.get("permute", 0.0), 4),
                     "inverse": lib.get("inv_chol"), "quantize": lib.get("gptq_quantize"),
-                    "pack": lib.get("pack"), "share_broadcast": per.get("share_s", 0.0)},
+                    "pack": lib.get("pack"), "share_broadcast": per.get("share_s", 0.0),
+                    "host_waiting_for_chains": per.get("host_wait_s", 0.0)},
                 "note": "rank 0; forward is measured on the main stream, the chain phases on side "
                         "streams that run beside it, collectives from issue to completion",
                 "hessian_tflops_executed": achieved,
@@ -841,6 +885,8 @@ def main():
             "gpu_launches": int(lt[0]), "roofline": roofline, "cpu_baseline": cpu}
         if phases:
             out["phases"] = phases
+        if is_model and args.linear_check:
+            out["linear_check"] = linear_check(spec, device, False) + linear_check(spec, device, True)
         emit(out)
     if world > 1:
         dist.destroy_process_group()

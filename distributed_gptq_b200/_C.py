@@ -41,6 +41,7 @@ SIGNATURES = {
     "dgq_hessian_prepare": (_I32, [_P, _I64, _P, _I64, _I32, _F, _F, _P, _P, _P, _I64, _P]),
     "dgq_permute_cols_f32": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _P, _P, _P]),
     "dgq_permute_cols_u8": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _P, _P]),
+    "dgq_permute_cols_u16": (_I32, [_P, _I64, _P, _I64, _I32, _I32, _P, _P]),
     "dgq_inv_chol_workspace_bytes": (_I64, [_I32]),
     "dgq_inv_chol_upper": (_I32, [_P, _I32, _I64, _P, _P, _I64, _P]),
     "dgq_gemm_f32": (_I32, [_P, _I64, _P, _I64, _I32, _P, _I64, _I32, _I32, _I32, _F, _F, _I32, _P, _P]),
@@ -262,6 +263,9 @@ def permute_cols(src: torch.Tensor, perm: Optional[torch.Tensor],
         elif src.dtype == torch.uint8:
             check(lib().dgq_permute_cols_u8(_ptr(src), src.stride(0), _ptr(dst), cols, rows, cols,
                                             _ptr(perm), _stream()), "permute_cols_u8")
+        elif src.dtype in (torch.float16, torch.bfloat16):
+            check(lib().dgq_permute_cols_u16(_ptr(src), src.stride(0), _ptr(dst), cols, rows, cols,
+                                             _ptr(perm), _stream()), "permute_cols_u16")
         else:
             raise TypeError(src.dtype)
     return dst

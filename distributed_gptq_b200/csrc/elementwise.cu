@@ -251,6 +251,18 @@ permute_cols_u8_kernel(const uint8_t* __restrict__ src, int64_t lds, uint8_t* __
   }
 }
 
+__global__ void __launch_bounds__(256)
+permute_cols_u16_kernel(const uint16_t* __restrict__ src, int64_t lds, uint16_t* __restrict__ dst,
+                        int64_t ldd, int rows, int cols, const int32_t* __restrict__ perm) {
+  const int64_t total = (int64_t)rows * cols;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = idx / cols;
+    int c = (int)(idx - r * cols);
+    dst[r * ldd + c] = src[r * lds + checked_index(perm, c, cols)];
+  }
+}
+
 bool valid_bits(int b) { return b == 2 || b == 3 || b == 4 || b == 8; }
 
 }  // namespace
@@ -364,5 +376,15 @@ DGQ_EXPORT int32_t dgq_permute_cols_u8(const uint8_t* src, int64_t lds, uint8_t*
   DGQ_REQUIRE(src && dst && perm && rows > 0 && cols > 0 && lds >= cols && ldd >= cols, DGQ_ERR_ARG);
   permute_cols_u8_kernel<<<dgq_grid((int64_t)rows * cols, 256), 256, 0, dgq_stream(stream)>>>(
       src, lds, dst, ldd, rows, cols, perm);
+  return dgq_launch_status();
+}
+
+DGQ_EXPORT int32_t dgq_permute_cols_u16(const void* src, int64_t lds, void* dst, int64_t ldd,
+                                        int32_t rows, int32_t cols, const int32_t* perm,
+                                        void* stream) {
+  DGQ_REQUIRE(src && dst && perm && rows > 0 && cols > 0 && lds >= cols && ldd >= cols, DGQ_ERR_ARG);
+  permute_cols_u16_kernel<<<dgq_grid((int64_t)rows * cols, 256), 256, 0, dgq_stream(stream)>>>(
+      reinterpret_cast<const uint16_t*>(src), lds, reinterpret_cast<uint16_t*>(dst), ldd, rows,
+      cols, perm);
   return dgq_launch_status();
 }

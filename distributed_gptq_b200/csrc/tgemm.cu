@@ -35,6 +35,16 @@ constexpr int BK = 32;                  // fp32 elements per slice = one 128-byt
 constexpr int OPERAND_BYTES = TILE * BK * 4;       // 16 KB
 constexpr int STAGE_BYTES = 4 * OPERAND_BYTES;     // A hi, A lo, B hi, B lo
 constexpr int STAGES = 3;
+// The tensor core adds into its fp32 accumulator with truncation, not rounding: measured on
+// B200, every 8-deep step of a product shrinks the sum by about 2^-25 of its value, always in
+// the same direction, so the relative error of a product grows linearly with the reduction
+// length (1e-6 at 128, 3e-5 at 4096 - a hundred times torch's fp32 product).  The reduction is
+// therefore cut into chunks of KC_SLICES slices when it is long (the inverse factor's products,
+// whose errors are amplified by the conditioning of the matrix); the epilogue warps add the
+// chunks' partial sums in registers with ordinary round-to-nearest fp32 additions, which bounds
+// the truncation error by that of one chunk whatever the length.
+constexpr int KC_SLICES = 4;            // 4 slices x 32 = 128 elements of k per chunk
+constexpr int CHUNK_FROM_K = 256;       // shorter reductions stay in tensor memory throughout
 constexpr int THREADS = 320;
 constexpr uint32_t TMEM_COLS = 256;                // two 128-column accumulators
 constexpr uint32_t TMEM_COLS_TS = 512;             // + per stage 32 columns of A hi and 32 of A lo
@@ -90,7 +100,8 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(r);
 }
 
-template <bool TS /* A operand of the products from tensor memory */>
+template <bool TS /* A operand of the products from tensor memory */,
+          bool CHUNKED /* reduction cut into chunks that are summed outside the tensor core */>
 __global__ void __launch_bounds__(THREADS, 1)
 tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const Params p) {
@@ -167,58 +178,66 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       const uint32_t idesc_nt = tc05::make_instr_desc(tc05::FMT_TF32, false, false, TILE, TILE);
       const uint32_t idesc_nn = tc05::make_instr_desc(tc05::FMT_TF32, false, true, TILE, TILE);
       const uint32_t idesc = p.b_is_kn ? idesc_nn : idesc_nt;
-      uint32_t it = 0, lt = 0;
+      uint32_t it = 0, ct = 0;   // slices and chunks issued so far
       bool ok = true;
-      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++lt) {
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
         const TileWork w = decode_tile(p, t);
-        const uint32_t ab = lt & 1, aph = (lt >> 1) & 1;
-        if (!tc05::mbar_wait_bounded(&ctl->tmem_empty[ab], aph ^ 1, abort_flag)) {
-          if (p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 12; }
-          break;
-        }
-        tc05::fence_after_sync();
-        const uint32_t acc = tmem_base + ab * TILE;
-        for (int s_ = 0; s_ < w.n_slices; ++s_, ++it) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-          if (!tc05::mbar_wait_bounded(&ctl->conv[s], ph, abort_flag)) {
-            if (p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 13; }
+        const int kc_len = CHUNKED ? KC_SLICES : w.n_slices;
+        for (int c0s = 0; c0s < w.n_slices && ok; c0s += kc_len, ++ct) {
+          // one chunk of the reduction into one of the two accumulators; the epilogue warps
+          // drain it while the next chunk goes into the other
+          const uint32_t ab = ct & 1, aph = (ct >> 1) & 1;
+          if (!tc05::mbar_wait_bounded(&ctl->tmem_empty[ab], aph ^ 1, abort_flag)) {
+            if (p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 12; }
             ok = false;
             break;
           }
           tc05::fence_after_sync();
-          const uint32_t a_hi = tc05::smem_u32(stages + (size_t)s * STAGE_BYTES);
-          const uint32_t a_lo = a_hi + OPERAND_BYTES;
-          const uint32_t b_hi = a_hi + 2 * OPERAND_BYTES;
-          const uint32_t b_lo = a_hi + 3 * OPERAND_BYTES;
-#pragma unroll
-          for (int k8 = 0; k8 < BK / 8; ++k8) {
-            // A (and B in NT form): rows of 128 bytes along k -> step 8 floats = 32 bytes
-            // B in NN form: four panels of 32 k-rows x 128 bytes -> step 8 rows = 1024 bytes
-            const uint32_t a_off = k8 * 32;
-            const uint32_t b_off = p.b_is_kn ? k8 * 1024 : k8 * 32;
-            // (n-contiguous fp32 uses the 32-byte-atom swizzle: groups of 4 k-rows, 512 bytes apart)
-            const uint32_t b_lbo = p.b_is_kn ? 32 * 128 : 0;
-            const uint32_t b_sbo = p.b_is_kn ? 512 : 1024;
-            const uint64_t b_layout = p.b_is_kn ? tc05::SWIZZLE_128B_BASE32B : tc05::SWIZZLE_128B;
-            const uint64_t da_hi = tc05::make_smem_desc(a_hi + a_off, 0, 1024);
-            const uint64_t da_lo = tc05::make_smem_desc(a_lo + a_off, 0, 1024);
-            const uint64_t db_hi = tc05::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_layout);
-            const uint64_t db_lo = tc05::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_layout);
-            if (TS) {
-              const uint32_t ta_hi = tmem_base + TS_A_COL0 + s * TS_A_STAGE_COLS + k8 * 8;
-              const uint32_t ta_lo = ta_hi + 32;
-              tc05::umma_tf32_ts(acc, ta_lo, db_hi, idesc, (s_ | k8) != 0 ? 1u : 0u);
-              tc05::umma_tf32_ts(acc, ta_hi, db_lo, idesc, 1u);
-              tc05::umma_tf32_ts(acc, ta_hi, db_hi, idesc, 1u);
-            } else {
-              tc05::umma_tf32(acc, da_lo, db_hi, idesc, (s_ | k8) != 0 ? 1u : 0u);
-              tc05::umma_tf32(acc, da_hi, db_lo, idesc, 1u);
-              tc05::umma_tf32(acc, da_hi, db_hi, idesc, 1u);
+          const uint32_t acc = tmem_base + ab * TILE;
+          const int s_end = min(w.n_slices, c0s + kc_len);
+          for (int s_ = c0s; s_ < s_end; ++s_, ++it) {
+            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+            if (!tc05::mbar_wait_bounded(&ctl->conv[s], ph, abort_flag)) {
+              if (p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 13; }
+              ok = false;
+              break;
             }
+            tc05::fence_after_sync();
+            const uint32_t a_hi = tc05::smem_u32(stages + (size_t)s * STAGE_BYTES);
+            const uint32_t a_lo = a_hi + OPERAND_BYTES;
+            const uint32_t b_hi = a_hi + 2 * OPERAND_BYTES;
+            const uint32_t b_lo = a_hi + 3 * OPERAND_BYTES;
+#pragma unroll
+            for (int k8 = 0; k8 < BK / 8; ++k8) {
+              // A (and B in NT form): rows of 128 bytes along k -> step 8 floats = 32 bytes
+              // B in NN form: four panels of 32 k-rows x 128 bytes -> step 8 rows = 1024 bytes
+              const uint32_t a_off = k8 * 32;
+              const uint32_t b_off = p.b_is_kn ? k8 * 1024 : k8 * 32;
+              // (n-contiguous fp32 uses the 32-byte-atom swizzle: groups of 4 k-rows, 512 bytes apart)
+              const uint32_t b_lbo = p.b_is_kn ? 32 * 128 : 0;
+              const uint32_t b_sbo = p.b_is_kn ? 512 : 1024;
+              const uint64_t b_layout = p.b_is_kn ? tc05::SWIZZLE_128B_BASE32B : tc05::SWIZZLE_128B;
+              const uint64_t da_hi = tc05::make_smem_desc(a_hi + a_off, 0, 1024);
+              const uint64_t da_lo = tc05::make_smem_desc(a_lo + a_off, 0, 1024);
+              const uint64_t db_hi = tc05::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_layout);
+              const uint64_t db_lo = tc05::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_layout);
+              const uint32_t first = (s_ != c0s || k8 != 0) ? 1u : 0u;   // 0: overwrite the accumulator
+              if (TS) {
+                const uint32_t ta_hi = tmem_base + TS_A_COL0 + s * TS_A_STAGE_COLS + k8 * 8;
+                const uint32_t ta_lo = ta_hi + 32;
+                tc05::umma_tf32_ts(acc, ta_lo, db_hi, idesc, first);
+                tc05::umma_tf32_ts(acc, ta_hi, db_lo, idesc, 1u);
+                tc05::umma_tf32_ts(acc, ta_hi, db_hi, idesc, 1u);
+              } else {
+                tc05::umma_tf32(acc, da_lo, db_hi, idesc, first);
+                tc05::umma_tf32(acc, da_hi, db_lo, idesc, 1u);
+                tc05::umma_tf32(acc, da_hi, db_hi, idesc, 1u);
+              }
+            }
+            tc05::umma_commit(&ctl->empty[s]);
           }
-          tc05::umma_commit(&ctl->empty[s]);
+          if (ok) tc05::umma_commit(&ctl->tmem_full[ab]);
         }
-        if (ok) tc05::umma_commit(&ctl->tmem_full[ab]);
       }
     }
     __syncwarp();
@@ -294,84 +313,176 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;
-    uint32_t lt = 0;
-    for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++lt) {
-      const TileWork w = decode_tile(p, t);
-      const uint32_t ab = lt & 1, aph = (lt >> 1) & 1;
-      const bool got = tc05::mbar_wait_bounded(&ctl->tmem_full[ab], aph, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0 && p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 15; }
-        break;
-      }
-      tc05::fence_after_sync();
-      // Each warp drains its 32 accumulator rows 32 columns at a time: TMEM -> registers
-      // (one row per lane) -> this warp's 4 KB of shared memory (16-byte pieces XOR-swizzled
-      // by the row so that neither side has bank conflicts) -> global memory with eight
-      // lanes per row, i.e. every load/store instruction touches four whole 128-byte lines.
-      float4* mine = reinterpret_cast<float4*>(epi_stage) + (warp - 6) * (32 * 8);
-      const int row0 = w.ti * TILE + q * 32;
-#pragma unroll 1
-      for (int chunk = 0; chunk < TILE / 32; ++chunk) {
-        const int c0 = w.tj * TILE + chunk * 32;
-        const bool live = (row0 < p.m && c0 < p.n);   // uniform across the warp
-        // this lane's eight 16-byte pieces of C: rows row0 + 4 it + lane/8, columns c0 + 4 (lane%8)
-        const int c = c0 + 4 * (lane & 7);
-        float4 old[8];
-        bool ok[8];
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int row = row0 + it * 4 + (lane >> 3);
-          // whole float4 inside the matrix (and, for a lower-triangular result, not right of
-          // the diagonal); ragged pieces take the scalar path below
-          ok[it] = live && row < p.m && c + 3 < p.n && (!p.lower_only || c + 3 <= row);
-          old[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if constexpr (!CHUNKED) {
+      // ---- short reductions: the whole sum stays in tensor memory, one drain per tile
+      const int q = warp & 3;
+      uint32_t lt = 0;
+      for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++lt) {
+        const TileWork w = decode_tile(p, t);
+        const uint32_t ab = lt & 1, aph = (lt >> 1) & 1;
+        const bool got = tc05::mbar_wait_bounded(&ctl->tmem_full[ab], aph, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0 && p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 15; }
+          break;
         }
-        if (p.beta != 0.f) {
-          // all loads of the chunk are issued before anything waits on them
-#pragma unroll
+        tc05::fence_after_sync();
+        // Each warp drains its 32 accumulator rows 32 columns at a time: TMEM -> registers
+        // (one row per lane) -> this warp's 4 KB of shared memory (16-byte pieces XOR-swizzled
+        // by the row so that neither side has bank conflicts) -> global memory with eight
+        // lanes per row, i.e. every load/store instruction touches four whole 128-byte lines.
+        float4* mine = reinterpret_cast<float4*>(epi_stage) + (warp - 6) * (32 * 8);
+        const int row0 = w.ti * TILE + q * 32;
+  #pragma unroll 1
+        for (int chunk = 0; chunk < TILE / 32; ++chunk) {
+          const int c0 = w.tj * TILE + chunk * 32;
+          const bool live = (row0 < p.m && c0 < p.n);   // uniform across the warp
+          // this lane's eight 16-byte pieces of C: rows row0 + 4 it + lane/8, columns c0 + 4 (lane%8)
+          const int c = c0 + 4 * (lane & 7);
+          float4 old[8];
+          bool ok[8];
+  #pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int row = row0 + it * 4 + (lane >> 3);
-            if (ok[it]) old[it] = *reinterpret_cast<const float4*>(p.c + (int64_t)row * p.ldc + c);
+            // whole float4 inside the matrix (and, for a lower-triangular result, not right of
+            // the diagonal); ragged pieces take the scalar path below
+            ok[it] = live && row < p.m && c + 3 < p.n && (!p.lower_only || c + 3 <= row);
+            old[it] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
-        }
-        uint32_t v[32];
-        tc05::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE + chunk * 32, v);
-        tc05::tmem_ld_wait();
-        if (!live) continue;
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4)
-          mine[lane * 8 + (c4 ^ (lane & 7))] =
-              make_float4(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]),
-                          __uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3]));
-        __syncwarp();
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int rr = it * 4 + (lane >> 3), c4 = lane & 7;
-          const int row = row0 + rr;
-          const float4 acc = mine[rr * 8 + (c4 ^ (rr & 7))];
-          float* cp = p.c + (int64_t)row * p.ldc + c;
-          if (ok[it]) {
-            *reinterpret_cast<float4*>(cp) =
-                make_float4(fmaf(p.alpha, acc.x, p.beta * old[it].x), fmaf(p.alpha, acc.y, p.beta * old[it].y),
-                            fmaf(p.alpha, acc.z, p.beta * old[it].z), fmaf(p.alpha, acc.w, p.beta * old[it].w));
-          } else if (row < p.m && c < p.n) {
-            const float o[4] = {acc.x, acc.y, acc.z, acc.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (c + e < p.n && (!p.lower_only || c + e <= row)) {
-                float val = p.alpha * o[e];
-                if (p.beta != 0.f) val += p.beta * cp[e];
-                cp[e] = val;
+          if (p.beta != 0.f) {
+            // all loads of the chunk are issued before anything waits on them
+  #pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int row = row0 + it * 4 + (lane >> 3);
+              if (ok[it]) old[it] = *reinterpret_cast<const float4*>(p.c + (int64_t)row * p.ldc + c);
+            }
+          }
+          uint32_t v[32];
+          tc05::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE + chunk * 32, v);
+          tc05::tmem_ld_wait();
+          if (!live) continue;
+  #pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4)
+            mine[lane * 8 + (c4 ^ (lane & 7))] =
+                make_float4(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]),
+                            __uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3]));
+          __syncwarp();
+  #pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3), c4 = lane & 7;
+            const int row = row0 + rr;
+            const float4 acc = mine[rr * 8 + (c4 ^ (rr & 7))];
+            float* cp = p.c + (int64_t)row * p.ldc + c;
+            if (ok[it]) {
+              *reinterpret_cast<float4*>(cp) =
+                  make_float4(fmaf(p.alpha, acc.x, p.beta * old[it].x), fmaf(p.alpha, acc.y, p.beta * old[it].y),
+                              fmaf(p.alpha, acc.z, p.beta * old[it].z), fmaf(p.alpha, acc.w, p.beta * old[it].w));
+            } else if (row < p.m && c < p.n) {
+              const float o[4] = {acc.x, acc.y, acc.z, acc.w};
+  #pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (c + e < p.n && (!p.lower_only || c + e <= row)) {
+                  float val = p.alpha * o[e];
+                  if (p.beta != 0.f) val += p.beta * cp[e];
+                  cp[e] = val;
+                }
               }
             }
           }
+          __syncwarp();   // the staging rows are rewritten by the next chunk
         }
-        __syncwarp();   // the staging rows are rewritten by the next chunk
+        tc05::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc05::mbar_arrive(&ctl->tmem_empty[ab]);
       }
-      tc05::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) tc05::mbar_arrive(&ctl->tmem_empty[ab]);
+
+    } else {
+      // ---- long reductions: chunks of KC_SLICES slices, summed in registers
+      const int q = warp & 3;
+      uint32_t ct = 0;            // chunks drained so far
+      bool alive = true;
+      for (int t = blockIdx.x; t < p.n_tiles && alive; t += gridDim.x) {
+        const TileWork w = decode_tile(p, t);
+        // ---- this thread's row of the tile: the chunks' partial sums are added here
+        float acc[TILE];
+        const int n_chunks = (w.n_slices + KC_SLICES - 1) / KC_SLICES;
+        for (int kc = 0; kc < n_chunks; ++kc, ++ct) {
+          const uint32_t ab = ct & 1, aph = (ct >> 1) & 1;
+          const bool got = tc05::mbar_wait_bounded(&ctl->tmem_full[ab], aph, abort_flag);
+          if (!__all_sync(0xffffffffu, got)) {
+            if (lane == 0 && p.info) { p.info[0] = DGQ_INFO_WAIT_TIMEOUT; p.info[1] = 15; }
+            alive = false;
+            break;
+          }
+          tc05::fence_after_sync();
+          // 16 columns at a time: the row's 128 running sums already take most of the registers
+          // (ten warps share the register file, 168 registers per thread at most)
+  #pragma unroll
+          for (int piece = 0; piece < TILE / 16; ++piece) {
+            uint32_t v[16];
+            tc05::tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE + piece * 16, v);
+            tc05::tmem_ld_wait();
+            if (kc == 0) {
+  #pragma unroll
+              for (int j = 0; j < 16; ++j) acc[piece * 16 + j] = __uint_as_float(v[j]);
+            } else {
+  #pragma unroll
+              for (int j = 0; j < 16; ++j) acc[piece * 16 + j] += __uint_as_float(v[j]);
+            }
+          }
+          tc05::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc05::mbar_arrive(&ctl->tmem_empty[ab]);
+        }
+        if (!alive) break;
+        // ---- output.  Each warp writes its 32 rows 32 columns at a time: registers (one row
+        // per lane) -> this warp's 4 KB of shared memory (16-byte pieces XOR-swizzled by the row
+        // so that neither side has bank conflicts) -> global memory with eight lanes per row,
+        // i.e. every load/store instruction touches four whole 128-byte lines.
+        float4* mine = reinterpret_cast<float4*>(epi_stage) + (warp - 6) * (32 * 8);
+        const int row0 = w.ti * TILE + q * 32;
+  #pragma unroll
+        for (int chunk = 0; chunk < TILE / 32; ++chunk) {
+          const int c0 = w.tj * TILE + chunk * 32;
+          const bool live = (row0 < p.m && c0 < p.n);   // uniform across the warp
+          if (!live) continue;
+          // this lane's eight 16-byte pieces of C: rows row0 + 4 it + lane/8, columns c0 + 4 (lane%8)
+          const int c = c0 + 4 * (lane & 7);
+  #pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4)
+            mine[lane * 8 + (c4 ^ (lane & 7))] =
+                make_float4(acc[chunk * 32 + 4 * c4], acc[chunk * 32 + 4 * c4 + 1],
+                            acc[chunk * 32 + 4 * c4 + 2], acc[chunk * 32 + 4 * c4 + 3]);
+          __syncwarp();
+  #pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3), c4 = lane & 7;
+            const int row = row0 + rr;
+            const float4 a4 = mine[rr * 8 + (c4 ^ (rr & 7))];
+            float* cp = p.c + (int64_t)row * p.ldc + c;
+            // whole float4 inside the matrix (and, for a lower-triangular result, not right of
+            // the diagonal); ragged pieces take the scalar path below
+            if (row < p.m && c + 3 < p.n && (!p.lower_only || c + 3 <= row)) {
+              float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.beta != 0.f) o = *reinterpret_cast<const float4*>(cp);
+              *reinterpret_cast<float4*>(cp) =
+                  make_float4(fmaf(p.alpha, a4.x, p.beta * o.x), fmaf(p.alpha, a4.y, p.beta * o.y),
+                              fmaf(p.alpha, a4.z, p.beta * o.z), fmaf(p.alpha, a4.w, p.beta * o.w));
+            } else if (row < p.m && c < p.n) {
+              const float o[4] = {a4.x, a4.y, a4.z, a4.w};
+  #pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (c + e < p.n && (!p.lower_only || c + e <= row)) {
+                  float val = p.alpha * o[e];
+                  if (p.beta != 0.f) val += p.beta * cp[e];
+                  cp[e] = val;
+                }
+              }
+            }
+          }
+          __syncwarp();   // the staging rows are rewritten by the next chunk
+        }
+      }
+
     }
   }
 
@@ -402,8 +513,10 @@ bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
   static DgqDeviceOnce once;
   if (!once.run([] {
         const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
-        return cudaFuncSetAttribute(tgemm_kernel<false>, at, (int)SMEM_BYTES) == cudaSuccess &&
-               cudaFuncSetAttribute(tgemm_kernel<true>, at, (int)SMEM_BYTES) == cudaSuccess;
+        return cudaFuncSetAttribute(tgemm_kernel<false, false>, at, (int)SMEM_BYTES) == cudaSuccess &&
+               cudaFuncSetAttribute(tgemm_kernel<true, false>, at, (int)SMEM_BYTES) == cudaSuccess &&
+               cudaFuncSetAttribute(tgemm_kernel<false, true>, at, (int)SMEM_BYTES) == cudaSuccess &&
+               cudaFuncSetAttribute(tgemm_kernel<true, true>, at, (int)SMEM_BYTES) == cudaSuccess;
       }))
     return false;
   CUtensorMap map_a, map_b;
@@ -439,9 +552,17 @@ bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
     const char* v = std::getenv("DGQ_TGEMM_SS");
     return !(v && v[0] != '\0' && v[0] != '0');
   }();
-  const cudaError_t e = a_from_tmem
-      ? dgq_launch_chained(tgemm_kernel<true>, dim3(grid), dim3(THREADS), SMEM_BYTES, st, map_a, map_b, p)
-      : dgq_launch_chained(tgemm_kernel<false>, dim3(grid), dim3(THREADS), SMEM_BYTES, st, map_a, map_b, p);
+  // reductions longer than CHUNK_FROM_K are cut into chunks (see KC_SLICES): up to that length
+  // the accumulator's truncation stays below 2e-6 of the result, beyond it it would keep growing
+  const bool chunked = g.k > CHUNK_FROM_K;
+  const dim3 gd(grid), bd(THREADS);
+  cudaError_t e;
+  if (a_from_tmem)
+    e = chunked ? dgq_launch_chained(tgemm_kernel<true, true>, gd, bd, SMEM_BYTES, st, map_a, map_b, p)
+                : dgq_launch_chained(tgemm_kernel<true, false>, gd, bd, SMEM_BYTES, st, map_a, map_b, p);
+  else
+    e = chunked ? dgq_launch_chained(tgemm_kernel<false, true>, gd, bd, SMEM_BYTES, st, map_a, map_b, p)
+                : dgq_launch_chained(tgemm_kernel<false, false>, gd, bd, SMEM_BYTES, st, map_a, map_b, p);
   dgq_note_launches(1);
   return e == cudaSuccess && cudaGetLastError() == cudaSuccess;
 }

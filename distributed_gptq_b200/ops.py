@@ -13,6 +13,13 @@ runs of ``in_features // n_groups`` consecutive columns, which is what the
 reference's own dequantize-and-matmul branch computes.  A ``g_idx`` that is exactly
 that sequential map is not passed on either, so that such layers take the kernel's
 tensor-core path.
+
+Act-order checkpoints carry a general map: every group has ``group_size`` columns, scattered
+over the row.  For those (4-bit, ``group_size`` a multiple of 128) the columns are brought into
+group order once per weight buffer - the reordered packed weights and the column order are
+kept on the buffer object, which costs a second copy of the packed weights - and every call
+gathers its activations into the same order, after which the layer is a sequential one and
+takes the same path.
 """
 from __future__ import annotations
 
@@ -53,6 +60,30 @@ def _g_idx_usable(g_idx: torch.Tensor, n_groups: int) -> bool:
     return _classify_g_idx(g_idx, n_groups) != _INVALID
 
 
+def _grouped_layout(qweight: torch.Tensor, g_idx: torch.Tensor, n_groups: int, K: int):
+    """For a general ``g_idx`` whose groups all have the same size: ``(qweight with its columns
+    in group order, the column order)``, computed once per pair of buffers; ``None`` when the
+    groups are uneven."""
+    tag = getattr(qweight, "_dgq_grouped", None)
+    if tag is not None and tag[0] == (qweight._version, g_idx.data_ptr(), g_idx._version):
+        return tag[1]
+    group_size = K // n_groups
+    out = None
+    if n_groups * group_size == K:
+        gi = g_idx.reshape(-1).long()
+        counts = torch.bincount(gi, minlength=n_groups)
+        if bool((counts == group_size).all()):
+            order = torch.argsort(gi, stable=True).to(torch.int32)
+            codes = _C.unpack(qweight, K, 4, _C.FMT_BYTES_LO_FIRST)
+            grouped = _C.pack(_C.permute_cols(codes, order), 4, _C.FMT_BYTES_LO_FIRST)
+            out = (grouped, order)
+    try:
+        qweight._dgq_grouped = ((qweight._version, g_idx.data_ptr(), g_idx._version), out)
+    except AttributeError:
+        pass
+    return out
+
+
 def gptq_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
                 g_idx: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
     K = g_idx.numel()
@@ -64,6 +95,17 @@ def gptq_linear(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, ze
     n_groups = scales.shape[1]
     group_size = -(-K // n_groups)
     gi = g_idx if _classify_g_idx(g_idx, n_groups) == _GENERAL else None
+    if (gi is not None and four_bit and K % 128 == 0 and group_size % 128 == 0 and
+            x.dtype in (torch.float16, torch.bfloat16)):
+        layout = _grouped_layout(qweight, g_idx, n_groups, K)
+        if layout is not None:
+            grouped, order = layout
+            x2 = x.reshape(-1, K)
+            if x2.stride(-1) != 1:
+                x2 = x2.contiguous()
+            xg = _C.permute_cols(x2, order)
+            y = _C.qlinear_forward(xg, grouped, scales, zeros, None, bias, K, 4, group_size)
+            return y.reshape(*x.shape[:-1], y.shape[-1])
     return _C.qlinear_forward(x, qweight, scales, zeros, gi, bias, K, 4 if four_bit else 8,
                               group_size)
 

@@ -840,7 +840,10 @@ class DistributedGPTQuantizer:
 
     def _collect(self, item) -> None:
         b, names_b, targets, groups, shared, shard = item
+        t0 = time.perf_counter()
         results = self._finalize(names_b, targets, groups, shared)
+        # how long the host stood still for this block's chains (it runs ahead otherwise)
+        self.timings["host_wait_s"] = self.timings.get("host_wait_s", 0.0) + time.perf_counter() - t0
         if shard is not None and self.dist_config.rank == 0:
             io.save_block_shard(shard, names_b, targets, results,
                                 {n: self._leader[n] for n in names_b}, self.quant_config)

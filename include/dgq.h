@@ -108,6 +108,8 @@ int32_t dgq_cast_f16_to_bf16(const void* src_f16, void* dst_bf16, int64_t n, voi
  *   receives the dead mask.  H and Hout must not overlap.  ws: 256 bytes.
  * dgq_permute_cols_f32: dst[r][i] = dead && dead[i] ? 0 : src[r][perm[i]]
  * dgq_permute_cols_u8 : dst[r][i] = src[r][perm[i]]
+ * dgq_permute_cols_u16: the same for 16-bit elements (fp16 / bf16 activations brought into the
+ *   column order of an act-order layer before the quantized linear, models/layers.py:150-153)
  */
 int32_t dgq_actorder_perm(const float* H, int32_t K, int64_t ldh, float scale,
                           int32_t* perm, int32_t* invperm, void* stream);
@@ -120,6 +122,8 @@ int32_t dgq_permute_cols_f32(const float* src, int64_t lds, float* dst, int64_t 
                              const uint8_t* dead, void* stream);
 int32_t dgq_permute_cols_u8(const uint8_t* src, int64_t lds, uint8_t* dst, int64_t ldd,
                             int32_t rows, int32_t cols, const int32_t* perm, void* stream);
+int32_t dgq_permute_cols_u16(const void* src, int64_t lds, void* dst, int64_t ldd,
+                             int32_t rows, int32_t cols, const int32_t* perm, void* stream);
 
 /* ---- damped inverse -------------------------------------------------------
  * Replaces core/gptq.py:121-122 (`cholesky_inverse(linalg.cholesky(H))`) and the

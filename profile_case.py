@@ -6,6 +6,7 @@
     python profile_case.py pack      --K 8192 --N 16384
     python profile_case.py dequant   --K 8192 --N 16384
     python profile_case.py qlinear   --K 5120 --N 5120 --M 16
+    python profile_case.py gemm      --K 4096 --N 4096 --T 4096     (m = T, n = N, k = K)
 
 Prints the CUDA-event time of each repetition and the derived rate (algorithmic flops
 or bytes over time).  Sizes default to a few hundred MB so that a profiler capture ends
@@ -52,7 +53,7 @@ def _time_raw(call, reps, inner=50):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["hessian", "inv_chol", "quantize", "pack", "dequant", "qlinear"])
+    ap.add_argument("case", choices=["hessian", "inv_chol", "quantize", "pack", "dequant", "qlinear", "gemm"])
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--T", type=int, default=32768)
@@ -60,6 +61,8 @@ def main():
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--upper", action="store_true",
+                    help="hessian: update only the part on and above the diagonal")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -69,12 +72,22 @@ def main():
     if a.case == "hessian":
         X = torch.randn(T, K, generator=g, device=dev).to(torch.bfloat16)
         H = torch.zeros((K, K), dtype=torch.float32, device=dev)
-        ts = _time(lambda: _C.hessian_accum(X, H, 1.0, a.splits), a.reps)
+        ts = _time(lambda: _C.hessian_accum(X, H, 1.0, a.splits, upper_only=a.upper), a.reps)
         P = -(-K // 256)
         ex = (P * (P + 1) // 2) * 2.0 * 256 * 256 * T
         for t in ts:
             print(f"hessian K={K} T={T}: {t:.3f} ms  executed {ex / t / 1e9:.1f} TFLOP/s  "
                   f"algorithmic {2.0 * T * K * K / t / 1e9:.1f} TFLOP/s")
+    elif a.case == "gemm":
+        m = T
+        A = torch.randn(m, K, generator=g, device=dev)
+        B = torch.randn(N, K, generator=g, device=dev)
+        C = torch.empty(m, N, device=dev)
+        want = A.double() @ B.double().t()
+        for t in _time(lambda: _C.gemm_f32(A, B, C, False), a.reps):
+            err = float((C.double() - want).norm() / want.norm())
+            print(f"gemm_f32 m={m} n={N} k={K}: {t:.3f} ms  {2.0 * m * N * K / t / 1e9:.1f} TFLOP/s "
+                  f"fp32-equivalent  rel. error vs fp64 {err:.2e}")
     elif a.case in ("inv_chol", "quantize"):
         X = torch.randn(2 * K, K, generator=g, device=dev).to(torch.bfloat16)
         H = torch.zeros((K, K), dtype=torch.float32, device=dev)

@@ -221,3 +221,17 @@ def test_share_layout_is_aligned_and_deterministic():
                         qz._piece(flat, p[4], p[5], p[6]).element_size()) for p in pieces)
         assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
         assert qz._share_layout([g1, g2], 1) == (pieces, total)
+
+
+def test_command_line_surface():
+    """Option names, defaults and choices of the reference's `quantize` command (cli.py:130-300)."""
+    from distributed_gptq_b200 import cli
+    a = cli.create_parser().parse_args(["quantize", "--model", "m"])
+    assert (a.bits, a.group_size, a.damp, a.num_samples, a.seq_len, a.batch_size, a.dataset,
+            a.torch_dtype, a.output_dir, a.act_order, a.true_sequential) == \
+        (4, 128, 0.01, 128, 2048, 1, "wikitext", "float16", "./quantized_models", False, False)
+    import pytest
+    with pytest.raises(SystemExit):
+        cli.create_parser().parse_args(["quantize", "--model", "m", "--bits", "5"])
+    b = cli.create_parser().parse_args(["benchmark", "--model", "m", "--quantized-model", "q"])
+    assert b.device == "cuda" and b.func is cli.benchmark_command

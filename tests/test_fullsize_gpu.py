@@ -108,8 +108,16 @@ def test_codes_match_oracle_on_a_row_slice(dgq, N_out, K, bits, act):
     diff = (codes.int() - ref["codes"].int()).abs()
     match = float((diff == 0).float().mean())
     assert match >= 0.995, match
-    assert int(diff.max()) <= 1
     assert torch.equal(q.g_idx.cpu(), ref["g_idx"])
+    # "Adjacent levels" is judged on the level a code stands for, code - zero: when a group's
+    # range moves by a rounding error its zero point may come out one higher or lower, which
+    # shifts every code of the group by one while the values they stand for stay put.
+    gi_cpu = ref["g_idx"].long()
+    z_gpu, z_ref = q.zero[rows.cuda()].cpu(), ref["zero"]
+    level_diff = (codes.float() - z_gpu[:, gi_cpu]) - (ref["codes"].float() - z_ref[:, gi_cpu])
+    assert float(level_diff.abs().max()) <= 1
+    assert float((z_gpu != z_ref).float().mean()) <= 0.01
+    assert int(diff.max()) <= 2
     Q = lin.weight.data.float().cpu()[rows]
     r_gpu, r_ref = O.recon_error(W0[rows], Q, H_raw), O.recon_error(W0[rows], ref["Q"], H_raw)
     assert abs(r_gpu - r_ref) <= 0.02 * r_ref, (r_gpu, r_ref)

@@ -4,8 +4,10 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-# relative Frobenius error allowed: three tf32 products of a hi/lo split keep ~2^-21 per term
-TOL = 5e-6
+# Relative Frobenius error allowed.  Three tf32 products of a hi/lo split keep ~2^-21 per
+# term; the tensor core's accumulator truncates, which the kernel confines to chunks of 128
+# along k (the chunks are summed with rounding), so the error must not grow with k.
+TOL = 2.5e-6
 
 
 def _rel(a, b):
@@ -13,7 +15,8 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 32), (128, 128, 128), (256, 384, 512), (200, 132, 72),
-                                   (1000, 520, 264), (4096, 1024, 128), (130, 4096, 128)])
+                                   (1000, 520, 264), (4096, 1024, 128), (130, 4096, 128),
+                                   (512, 384, 4096), (256, 256, 11008)])
 @pytest.mark.parametrize("b_is_kn", [False, True])
 def test_gemm_matches_fp64(dgq, m, n, k, b_is_kn):
     g = torch.Generator(device="cuda").manual_seed(m + n + k)
@@ -28,6 +31,8 @@ def test_gemm_matches_fp64(dgq, m, n, k, b_is_kn):
     assert _rel(c, want) <= TOL
     ref32 = -0.5 * (a @ (b if b_is_kn else b.t())) + 2.0 * c0
     assert _rel(c, want) <= 20 * max(_rel(ref32, want), 1e-8)
+    if k >= 4096:       # long reductions: as accurate as torch's fp32 product, within a small factor
+        assert _rel(c, want) <= 3 * _rel(ref32, want)
     # beta = 0 must not read C (NaNs in C stay out of the result)
     c = torch.full((m, n), float("nan"), device="cuda")
     dgq.gemm_f32(a, b, c, b_is_kn)

@@ -161,3 +161,29 @@ def test_kernels_module(dgq):
     assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
     d = dequantize_tensor(q, s, z, 128)
     assert torch.equal(d.cpu(), O.rtn_dequantize(qo, so, zo, 128))
+
+
+def test_command_line_quantize_and_benchmark(dgq, tmp_path, capsys):
+    """`quantize` then `benchmark` of the command line (reference cli.py:36-95) on a small
+    Llama-architecture model given by its config alone."""
+    transformers = pytest.importorskip("transformers")
+    from distributed_gptq_b200 import cli
+    mdir, out = tmp_path / "model", tmp_path / "out"
+    transformers.LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512,
+                             num_hidden_layers=2, num_attention_heads=4,
+                             max_position_embeddings=256).save_pretrained(str(mdir))
+    torch.manual_seed(0)
+    cli.main(["quantize", "--model", str(mdir), "--torch-dtype", "bfloat16", "--bits", "4",
+              "--group-size", "128", "--act-order", "--dataset", "random", "--num-samples", "8",
+              "--seq-len", "96", "--batch-size", "4", "--output-dir", str(out)])
+    metrics = json.load(open(out / "quantization_metrics.json"))
+    assert metrics["layers"] == 14 and metrics["mode"] == "block-wise" and metrics["bits"] == 4
+    meta = json.load(open(out / "model.json"))
+    assert len(meta["quantized_layers"]) == 14 and "lm_head" not in meta["quantized_layers"]
+    torch.manual_seed(0)        # the same random weights for the float side of the comparison
+    cli.main(["benchmark", "--model", str(mdir), "--quantized-model", str(out / "model.safetensors"),
+              "--torch-dtype", "bfloat16", "--test-samples", "4", "--seq-len", "64",
+              "--save-results", str(out / "bench.json")])
+    res = json.load(open(out / "bench.json"))
+    assert res["compression_ratio"] > 1.5 and res["quantized"]["perplexity"] > 0
+    assert "Compression Ratio" in capsys.readouterr().out

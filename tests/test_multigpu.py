@@ -24,7 +24,16 @@ def _calib():
     return [torch.randn(2, 32, 256, generator=g) for _ in range(8)]
 
 
-def _run(rank, world, port, mode, out_path):
+def _decoder(sequential):
+    """A model with a list of blocks (block-by-block calibration) and a head outside it."""
+    from tests.test_blockwise_gpu import _ids, _model as decoder_model
+    from distributed_gptq_b200 import QuantizationConfig
+    cfg = QuantizationConfig(bits=4, group_size=128, actorder=False, calibration_samples=24,
+                             true_sequential=sequential)
+    return decoder_model(), _ids(), cfg
+
+
+def _run(rank, world, port, mode, out_path, kind="mlp"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
                       WORLD_SIZE=str(world), LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
     from distributed_gptq_b200 import DistributedGPTQuantizer, QuantizationConfig
@@ -33,9 +42,14 @@ def _run(rank, world, port, mode, out_path):
     dcfg.master_addr = "127.0.0.1"
     dcfg.init_timeout = 120
     dcfg.hessian_exchange = mode
-    qz = DistributedGPTQuantizer(QuantizationConfig(bits=4, group_size=128, actorder=False,
-                                                    calibration_samples=16), dcfg)
-    model = qz.quantize_model(_model(), _calib())
+    if kind == "mlp":
+        net, calib = _model(), _calib()
+        qcfg = QuantizationConfig(bits=4, group_size=128, actorder=False, calibration_samples=16)
+    else:
+        net, calib, qcfg = _decoder(kind == "decoder-sequential")
+    qz = DistributedGPTQuantizer(qcfg, dcfg, calibration_batch_size=4)
+    model = qz.quantize_model(net, calib)
+    assert kind == "mlp" or qz.mode_used.startswith("block-wise")
     state = {k: v.detach().cpu() for k, v in model.state_dict().items()}
     packed = {n: {k: v.cpu() for k, v in e.items()} for n, e in qz.packed.items()}
     torch.save({"state": state, "packed": packed, "errors": qz.quantization_errors},
@@ -84,3 +98,70 @@ def test_two_ranks_match_one(dgq, tmp_path, mode):
         assert float(far) < 0.02, (name, float(far))
         assert float((a - b).abs().max()) <= 0.2 * float(b.abs().max())
     assert set(res[0]["errors"]) == {"0", "2", "4"}
+
+
+@pytest.mark.parametrize("kind,mode", [("decoder", "owner"), ("decoder", "all_reduce"),
+                                       ("decoder-sequential", "owner")])
+def test_two_ranks_block_by_block(dgq, tmp_path, kind, mode):
+    """The block-by-block driver on two ranks: per-block reduce to the owner, chains on the
+    owners, one flat broadcast per owner and block; true-sequential re-runs every block with
+    the weights it received.  Both ranks must end with the same model, equal to the
+    single-GPU result up to the summation order of the partial Hessians."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from distributed_gptq_b200 import DistributedGPTQuantizer
+    from distributed_gptq_b200.coordinator import DistributedConfig
+    net, calib, qcfg = _decoder(kind == "decoder-sequential")
+    single = DistributedGPTQuantizer(qcfg, DistributedConfig(), calibration_batch_size=4)
+    ref = single.quantize_model(net, calib)
+    ref_state = {k: v.detach().cpu() for k, v in ref.state_dict().items()}
+    out = str(tmp_path / f"res_{kind}_{mode}")
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_run, args=(r, 2, port, mode, out, kind)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    res = [torch.load(f"{out}.{r}") for r in range(2)]
+    assert len(res[0]["packed"]) == 16 and set(res[0]["errors"]) == set(single.quantization_errors)
+    for k in res[0]["state"]:
+        assert torch.equal(res[0]["state"][k], res[1]["state"][k]), k
+    for n in res[0]["packed"]:
+        for k in res[0]["packed"][n]:
+            assert torch.equal(res[0]["packed"][n][k], res[1]["packed"][n][k]), k
+        assert res[0]["errors"][n] == res[1]["errors"][n]
+    for name, b in ref_state.items():
+        if not name.endswith("weight") or b.dim() != 2 or "embed" in name:
+            continue
+        a, b = res[0]["state"][name].float(), b.float()
+        far = ((a - b).abs() > 1e-4 * float(b.abs().max())).float().mean()
+        assert float(far) < 0.03, (name, float(far))
+
+
+def test_two_devices_in_one_process(dgq):
+    """One process that drives two GPUs (the reference's GPTQMultiGPU pattern,
+    core/gptq.py:269-341): kernel attributes and cached device properties are per device, so
+    the second device must work after the first has been used, with the same results."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from distributed_gptq_b200 import GPTQ
+    torch.manual_seed(0)
+    W = torch.randn(320, 512) * 0.02
+    X = torch.randn(4, 384, 512)
+    out = []
+    for dev in ("cuda:0", "cuda:1", "cuda:0"):
+        lin = nn.Linear(512, 320, bias=False)
+        lin.weight.data = W.clone()
+        lin = lin.to(dev)
+        q = GPTQ(lin, bits=4, group_size=128, actorder=True, device=dev)
+        q.add_batch(X.to(dev), None)
+        q.quantize()
+        packed = q.pack_weights(format=dgq.FMT_BYTES_LO_FIRST)["packed_weights"]
+        x = torch.randn(3, 512, generator=torch.Generator().manual_seed(1)).to(dev).half()
+        y = dgq.qlinear_forward(x, packed, q.scale.half(), q.zero.half(), q.g_idx, None, 512, 4, 128)
+        out.append((q.codes.cpu(), lin.weight.data.cpu(), y.cpu()))
+    for o in out[1:]:
+        assert torch.equal(o[0], out[0][0]) and torch.equal(o[1], out[0][1])
+        assert torch.equal(o[2], out[0][2])

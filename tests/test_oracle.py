@@ -156,3 +156,46 @@ def test_live_reference_add_batch():
     q.add_batch(x, None)
     H, n = O.hessian_add_batch(None, 0, x)
     assert n == q.nsamples and torch.equal(H, q.H)
+
+
+@pytest.mark.skipif(not ref_shim.available(), reason="reference tree not present")
+def test_reference_quantized_linear_forward_reaches_the_registered_operator():
+    """The reference's unmodified ``QuantizedLinear.forward`` (models/layers.py:140-157) calls
+    ``torch.ops.gptq.linear(x, qweight, scales, zeros, g_idx, bias)`` as soon as that operator
+    exists.  Importing this package defines it (schema in ``ops.py``; the CUDA kernel is bound
+    for CUDA tensors).  Here, on the CPU, a stand-in implementation built from the oracle is
+    bound for CPU tensors, and the reference class - its own buffers, filled by its own
+    ``pack_weights`` - must dispatch into it with the arguments in the schema's order and
+    return ``x @ unpack_weights().T + bias``."""
+    import distributed_gptq_b200  # noqa: F401  (defines gptq::linear)
+    L = ref_shim.load_layers()
+    calls = []
+
+    def cpu_impl(x, qweight, scales, zeros, g_idx, bias):
+        calls.append((tuple(x.shape), qweight.dtype, tuple(scales.shape), g_idx.numel(),
+                      bias is not None))
+        K = g_idx.numel()
+        codes = O.unpack_f2(qweight, 4, K)
+        group = K // scales.shape[1]
+        # the reference's default g_idx (0..K-1) holds no valid group numbers: sequential groups
+        gi = g_idx if int(g_idx.max()) < scales.shape[1] else None
+        return O.qlinear_forward(x, codes, scales, zeros, gi, bias, group).to(x.dtype)
+
+    lib = torch.library.Library("gptq", "IMPL", "CPU")
+    lib.impl("linear", cpu_impl)
+    g = torch.Generator().manual_seed(0)
+    N_out, K, group = 24, 256, 64
+    layer = L.QuantizedLinear(bits=4, group_size=group, in_features=K, out_features=N_out, bias=True)
+    codes = torch.randint(0, 16, (N_out, K), generator=g).to(torch.uint8)
+    scales = (torch.rand(N_out, K // group, generator=g) * 0.02 + 0.001).half()
+    zeros = torch.randint(0, 16, (N_out, K // group), generator=g).half()
+    layer.pack_weights(codes, scales, zeros)
+    layer.bias.data = torch.randn(N_out, generator=g)
+    x = torch.randn(3, 5, K, generator=g)
+    with torch.no_grad():
+        y = layer.forward(x)
+        want = x @ layer.unpack_weights().t() + layer.bias
+    assert calls == [((3, 5, K), torch.uint8, (N_out, K // group), K, True)]
+    assert tuple(y.shape) == (3, 5, N_out)
+    assert torch.allclose(y, want, rtol=1e-5, atol=1e-5)
+    del lib

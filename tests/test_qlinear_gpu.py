@@ -63,3 +63,37 @@ def test_qlinear_tensor_core_path(dgq, M, N_out, K, g, dtype, integer_zeros):
     if not integer_zeros:
         tol *= 2
     assert float((got.float().cpu() - want).abs().max()) <= tol * float(want.abs().max())
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 40])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_operator_with_act_order_checkpoint(dgq, M, dtype):
+    """An act-order checkpoint through ``torch.ops.gptq.linear``: the group of a column is
+    arbitrary (every group still has 128 columns).  The operator brings the columns into group
+    order once and gathers the activations per call, so the result must be that of the
+    dequantize + matmul of models/layers.py:155-157 to the kernel's tolerance, call after call."""
+    import distributed_gptq_b200  # noqa: F401
+    N_out, K, g = 320, 1024, 128
+    gen = torch.Generator().manual_seed(M)
+    codes = torch.randint(0, 16, (N_out, K), generator=gen).to(torch.uint8)
+    scales = (torch.rand(N_out, K // g, generator=gen) * 0.02 + 0.001).half()
+    zeros = torch.randint(0, 16, (N_out, K // g), generator=gen).half()
+    g_idx = (torch.arange(K) // g).to(torch.int32)[torch.randperm(K, generator=gen)]
+    bias = torch.randn(N_out, generator=gen).to(dtype)
+    x = torch.randn(2, M, K, generator=gen).to(dtype)
+    want = O.qlinear_forward(x.reshape(-1, K), codes, scales, zeros, g_idx, bias, g).reshape(2, M, N_out)
+    qw, s, z, gi, b = (t.cuda() for t in (O.pack_f2(codes, 4), scales, zeros, g_idx, bias))
+    n0 = dgq.launch_count()
+    for _ in range(2):      # the second call finds the reordered weights on the buffer
+        got = torch.ops.gptq.linear(x.cuda(), qw, s, z, gi, b)
+        assert got.dtype == dtype and tuple(got.shape) == (2, M, N_out)
+        tol = {torch.float16: 6e-4, torch.bfloat16: 4.5e-3}[dtype]
+        assert float((got.float().cpu() - want).abs().max()) <= tol * float(want.abs().max())
+    assert hasattr(qw, "_dgq_grouped") and dgq.launch_count() > n0
+    # uneven groups cannot be reordered into whole groups: the general kernel takes them
+    odd = g_idx.clone()
+    odd[odd == 1] = 0
+    want2 = O.qlinear_forward(x.reshape(-1, K), codes, scales, zeros, odd, bias, g).reshape(2, M, N_out)
+    got2 = torch.ops.gptq.linear(x.cuda(), qw.clone(), s, z, odd.cuda(), b)
+    tol = {torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype]
+    assert float((got2.float().cpu() - want2).abs().max()) <= tol * float(want2.abs().max())

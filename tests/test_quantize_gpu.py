@@ -197,8 +197,14 @@ def test_wide_groups_see_all_earlier_updates(dgq, K, g, ws_cols):
     ws = None if ws_cols is None else N_out * ws_cols * 4
     codes, s, z, terr = dgq.gptq_quantize(Wd, U, 4, g, 128, ws_bytes=ws)
     d = (codes.cpu().int() - ref["codes"].int()).abs()
-    assert float((d == 0).float().mean()) >= CODE_MATCH and int(d.max()) <= 1
-    assert torch.allclose(s.cpu(), ref["scale"], rtol=1e-3, atol=0)
+    assert float((d == 0).float().mean()) >= 0.999 and int(d.max()) <= 1
+    # A row in which one code differs (a value within rounding of a level boundary) carries a
+    # different error into all later columns, so its later groups' ranges differ a little too:
+    # the scales are compared on the rows whose codes all agree, which must be nearly all.
+    same = d.sum(1) == 0
+    assert float(same.float().mean()) >= 0.95
+    assert torch.allclose(s.cpu()[same], ref["scale"][same], rtol=1e-5, atol=0)
+    assert torch.equal(z.cpu()[same], ref["zero"][same])
     assert abs(float(terr) - ref["total_error"]) <= 0.02 * ref["total_error"]
 
 
