@@ -382,8 +382,8 @@ struct Plan {
 // thread: calls on different streams must not share a side stream, or they would wait for
 // each other's products.  Depths do not share one either: the small product of a node deep
 // in the second half of the recursion would queue behind its ancestor's large one, and the
-// node's last product waits for it.  The table is small; when it is full an entry is taken over (stream
-// order keeps that correct, it only couples the two callers).
+// node's last product waits for it.  The table is small; when it is full an entry is taken
+// over (see side_resources).
 constexpr int SIDE_STREAMS = 10;
 struct SideResources {
   int device = -1;
@@ -392,44 +392,61 @@ struct SideResources {
   cudaEvent_t fork[32] = {}, join[32] = {};
   bool ok = false;
 };
+// Creates the entry's streams and events on the current device (same priority as the
+// caller's stream: the side products are on the chain's critical path).
+bool side_create(SideResources* r, int dev, cudaStream_t caller) {
+  int prio = 0;
+  if (cudaStreamGetPriority(caller, &prio) != cudaSuccess) prio = 0;
+  for (int d = 0; d < SIDE_STREAMS; ++d)
+    if (cudaStreamCreateWithPriority(&r->stream[d], cudaStreamNonBlocking, prio) != cudaSuccess)
+      return false;
+  for (int d = 0; d < 32; ++d) {
+    if (cudaEventCreateWithFlags(&r->fork[d], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&r->join[d], cudaEventDisableTiming) != cudaSuccess)
+      return false;
+  }
+  r->device = dev;
+  r->caller = caller;
+  r->ok = true;
+  return true;
+}
+
+// Releases an entry that belongs to another device (work already queued on its streams still
+// completes: destroying a stream only releases it once it has drained).
+void side_destroy(SideResources* r, int current_dev) {
+  if (!r->ok) return;
+  cudaSetDevice(r->device);
+  for (int d = 0; d < SIDE_STREAMS; ++d) cudaStreamDestroy(r->stream[d]);
+  for (int d = 0; d < 32; ++d) {
+    cudaEventDestroy(r->fork[d]);
+    cudaEventDestroy(r->join[d]);
+  }
+  cudaSetDevice(current_dev);
+  (void)cudaGetLastError();
+  *r = SideResources();
+}
+
 SideResources* side_resources(cudaStream_t caller) {
-  constexpr int SLOTS = 16;
+  constexpr int SLOTS = 32;
   thread_local SideResources table[SLOTS];
   thread_local int next_victim = 0;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  SideResources* r = nullptr;
-  for (int i = 0; i < SLOTS && !r; ++i)
-    if (table[i].ok && table[i].device == dev && table[i].caller == caller) r = &table[i];
-  for (int i = 0; i < SLOTS && !r; ++i)
-    if (!table[i].ok) r = &table[i];
-  if (!r) {
-    // take over an entry of the same device (its stream and events stay valid there)
-    for (int n = 0; n < SLOTS && !r; ++n) {
-      SideResources& c = table[(next_victim + n) % SLOTS];
-      if (c.device == dev) { r = &c; next_victim = (next_victim + n + 1) % SLOTS; }
-    }
-    if (!r) return nullptr;
+  for (int i = 0; i < SLOTS; ++i)
+    if (table[i].ok && table[i].device == dev && table[i].caller == caller) return &table[i];
+  for (int i = 0; i < SLOTS; ++i)
+    if (!table[i].ok) return side_create(&table[i], dev, caller) ? &table[i] : nullptr;
+  // The table is full: an entry is taken over.  One of the same device keeps its streams and
+  // events (stream order keeps that correct, it only couples the two callers); one of another
+  // device is released and made anew here.
+  SideResources* r = &table[next_victim];
+  next_victim = (next_victim + 1) % SLOTS;
+  if (r->device == dev) {
     r->caller = caller;
     return r;
   }
-  if (!r->ok) {
-    // same priority as the caller's stream: the side products are on the chain's critical path
-    int prio = 0;
-    if (cudaStreamGetPriority(caller, &prio) != cudaSuccess) prio = 0;
-    for (int d = 0; d < SIDE_STREAMS; ++d)
-      if (cudaStreamCreateWithPriority(&r->stream[d], cudaStreamNonBlocking, prio) != cudaSuccess)
-        return nullptr;
-    for (int d = 0; d < 32; ++d) {
-      if (cudaEventCreateWithFlags(&r->fork[d], cudaEventDisableTiming) != cudaSuccess ||
-          cudaEventCreateWithFlags(&r->join[d], cudaEventDisableTiming) != cudaSuccess)
-        return nullptr;
-    }
-    r->device = dev;
-    r->caller = caller;
-    r->ok = true;
-  }
-  return r;
+  side_destroy(r, dev);
+  return side_create(r, dev, caller) ? r : nullptr;
 }
 
 int split_point(int n) {

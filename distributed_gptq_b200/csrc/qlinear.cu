@@ -9,9 +9,11 @@
 // All accumulate up to 16 batch rows in fp32 and dequantize with the column's group
 // scale/zero (through g_idx when given).
 #include "common.cuh"
+#include "qlinear_tc.cuh"
 
 namespace {
 
+constexpr int TC_MIN_ROWS = 33;     // fewer rows of activations: the kernels below, 16 rows a launch
 constexpr int SLICE = 512;          // input columns staged per step
 constexpr int WARPS = 8;
 constexpr int ROWS_PER_WARP = 4;
@@ -660,6 +662,16 @@ DGQ_EXPORT int32_t dgq_qlinear_forward(const void* x, int32_t x_dtype, int32_t M
   a.vec16 = (a.row_bytes % 16 == 0 && dgq_aligned(qweight, 16)) ? 1 : 0;
   DGQ_REQUIRE(K % 8 != 0 || dgq_aligned(qweight, 8), DGQ_ERR_ALIGN);
   cudaStream_t st = dgq_stream(stream);
+  if (M >= TC_MIN_ROWS && bits == 4 && g_idx == nullptr && x_dtype != DGQ_F32) {
+    dgq::QLinearTcArgs t;
+    t.x = x; t.y = y; t.dtype = x_dtype; t.qw = qweight; t.row_bytes = a.row_bytes;
+    t.scales = a.scales; t.zeros = a.zeros; t.n_groups = n_groups; t.group_size = group_size;
+    t.bias = bias; t.bias_dtype = bias_dtype; t.M = M; t.N_out = N_out; t.K = K; t.info = nullptr;
+    if (dgq::qlinear_tc_supported(t) && dgq_device_check() == DGQ_OK) {
+      if (!dgq::qlinear_tc_launch(t, st)) return DGQ_ERR_LAUNCH;
+      return DGQ_OK;
+    }
+  }
   if (x_dtype == DGQ_F32) launch_all<float>(a, st);
   else if (x_dtype == DGQ_F16) launch_all<__half>(a, st);
   else launch_all<__nv_bfloat16>(a, st);

@@ -42,9 +42,16 @@ constexpr int STAGES = 3;
 // therefore cut into chunks of KC_SLICES slices when it is long (the inverse factor's products,
 // whose errors are amplified by the conditioning of the matrix); the epilogue warps add the
 // chunks' partial sums in registers with ordinary round-to-nearest fp32 additions, which bounds
-// the truncation error by that of one chunk whatever the length.
-constexpr int KC_SLICES = 4;            // 4 slices x 32 = 128 elements of k per chunk
-constexpr int CHUNK_FROM_K = 256;       // shorter reductions stay in tensor memory throughout
+// the truncation error by that of one chunk whatever the length.  A drain is not free: loads
+// from tensor memory queue behind the products already issued, so a chunk costs its products
+// plus about 1.3 us (measured: +35 % on a long product with chunks of 128, the price of an
+// inverse factor within 3x of LAPACK's fp32 accuracy).  Reductions up to 256 are left in one
+// piece (error <= 2e-6); the 512-deep trailing updates of the block quantization take two
+// chunks: their terms cancel to a result much smaller than their magnitudes, and with a
+// single chunk the truncation showed as code mismatches at K = 11008.
+constexpr int KC_SLICES = 4;            // long reductions: 4 slices x 32 = 128 elements of k per chunk
+constexpr int KC_SLICES_SHORT = 8;      // reductions of 257..512: two chunks of at most 256
+constexpr int CHUNK_FROM_K = 256;       // reductions up to this length stay in tensor memory throughout
 constexpr int THREADS = 320;
 constexpr uint32_t TMEM_COLS = 256;                // two 128-column accumulators
 constexpr uint32_t TMEM_COLS_TS = 512;             // + per stage 32 columns of A hi and 32 of A lo
@@ -65,6 +72,7 @@ struct Params {
   float alpha, beta;
   int b_is_kn, lo_from_j, hi_from_j, hi_from_i, lower_only;
   int tiles_m, tiles_n, n_tiles;
+  int kc_slices;         // slices per chunk of the reduction (chunked kernel)
   int32_t* info;
 };
 
@@ -182,7 +190,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       bool ok = true;
       for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
         const TileWork w = decode_tile(p, t);
-        const int kc_len = CHUNKED ? KC_SLICES : w.n_slices;
+        const int kc_len = CHUNKED ? p.kc_slices : w.n_slices;
         for (int c0s = 0; c0s < w.n_slices && ok; c0s += kc_len, ++ct) {
           // one chunk of the reduction into one of the two accumulators; the epilogue warps
           // drain it while the next chunk goes into the other
@@ -332,7 +340,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         // lanes per row, i.e. every load/store instruction touches four whole 128-byte lines.
         float4* mine = reinterpret_cast<float4*>(epi_stage) + (warp - 6) * (32 * 8);
         const int row0 = w.ti * TILE + q * 32;
-  #pragma unroll 1
+#pragma unroll 1
         for (int chunk = 0; chunk < TILE / 32; ++chunk) {
           const int c0 = w.tj * TILE + chunk * 32;
           const bool live = (row0 < p.m && c0 < p.n);   // uniform across the warp
@@ -340,7 +348,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           const int c = c0 + 4 * (lane & 7);
           float4 old[8];
           bool ok[8];
-  #pragma unroll
+#pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int row = row0 + it * 4 + (lane >> 3);
             // whole float4 inside the matrix (and, for a lower-triangular result, not right of
@@ -350,7 +358,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           }
           if (p.beta != 0.f) {
             // all loads of the chunk are issued before anything waits on them
-  #pragma unroll
+#pragma unroll
             for (int it = 0; it < 8; ++it) {
               const int row = row0 + it * 4 + (lane >> 3);
               if (ok[it]) old[it] = *reinterpret_cast<const float4*>(p.c + (int64_t)row * p.ldc + c);
@@ -360,13 +368,13 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           tc05::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE + chunk * 32, v);
           tc05::tmem_ld_wait();
           if (!live) continue;
-  #pragma unroll
+#pragma unroll
           for (int c4 = 0; c4 < 8; ++c4)
             mine[lane * 8 + (c4 ^ (lane & 7))] =
                 make_float4(__uint_as_float(v[4 * c4]), __uint_as_float(v[4 * c4 + 1]),
                             __uint_as_float(v[4 * c4 + 2]), __uint_as_float(v[4 * c4 + 3]));
           __syncwarp();
-  #pragma unroll
+#pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int rr = it * 4 + (lane >> 3), c4 = lane & 7;
             const int row = row0 + rr;
@@ -378,7 +386,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
                               fmaf(p.alpha, acc.z, p.beta * old[it].z), fmaf(p.alpha, acc.w, p.beta * old[it].w));
             } else if (row < p.m && c < p.n) {
               const float o[4] = {acc.x, acc.y, acc.z, acc.w};
-  #pragma unroll
+#pragma unroll
               for (int e = 0; e < 4; ++e) {
                 if (c + e < p.n && (!p.lower_only || c + e <= row)) {
                   float val = p.alpha * o[e];
@@ -404,7 +412,7 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         const TileWork w = decode_tile(p, t);
         // ---- this thread's row of the tile: the chunks' partial sums are added here
         float acc[TILE];
-        const int n_chunks = (w.n_slices + KC_SLICES - 1) / KC_SLICES;
+        const int n_chunks = (w.n_slices + p.kc_slices - 1) / p.kc_slices;
         for (int kc = 0; kc < n_chunks; ++kc, ++ct) {
           const uint32_t ab = ct & 1, aph = (ct >> 1) & 1;
           const bool got = tc05::mbar_wait_bounded(&ctl->tmem_full[ab], aph, abort_flag);
@@ -416,16 +424,16 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           tc05::fence_after_sync();
           // 16 columns at a time: the row's 128 running sums already take most of the registers
           // (ten warps share the register file, 168 registers per thread at most)
-  #pragma unroll
+#pragma unroll
           for (int piece = 0; piece < TILE / 16; ++piece) {
             uint32_t v[16];
             tc05::tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE + piece * 16, v);
             tc05::tmem_ld_wait();
             if (kc == 0) {
-  #pragma unroll
+#pragma unroll
               for (int j = 0; j < 16; ++j) acc[piece * 16 + j] = __uint_as_float(v[j]);
             } else {
-  #pragma unroll
+#pragma unroll
               for (int j = 0; j < 16; ++j) acc[piece * 16 + j] += __uint_as_float(v[j]);
             }
           }
@@ -440,36 +448,51 @@ tgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         // i.e. every load/store instruction touches four whole 128-byte lines.
         float4* mine = reinterpret_cast<float4*>(epi_stage) + (warp - 6) * (32 * 8);
         const int row0 = w.ti * TILE + q * 32;
-  #pragma unroll
+#pragma unroll
         for (int chunk = 0; chunk < TILE / 32; ++chunk) {
           const int c0 = w.tj * TILE + chunk * 32;
           const bool live = (row0 < p.m && c0 < p.n);   // uniform across the warp
           if (!live) continue;
           // this lane's eight 16-byte pieces of C: rows row0 + 4 it + lane/8, columns c0 + 4 (lane%8)
           const int c = c0 + 4 * (lane & 7);
-  #pragma unroll
+#pragma unroll
           for (int c4 = 0; c4 < 8; ++c4)
             mine[lane * 8 + (c4 ^ (lane & 7))] =
                 make_float4(acc[chunk * 32 + 4 * c4], acc[chunk * 32 + 4 * c4 + 1],
                             acc[chunk * 32 + 4 * c4 + 2], acc[chunk * 32 + 4 * c4 + 3]);
           __syncwarp();
-  #pragma unroll
+          // the chunk's 32 sums are in shared memory now and their registers are free: all
+          // loads of C are issued before anything waits on them
+          float4 old[8];
+          bool whole[8];
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int row = row0 + it * 4 + (lane >> 3);
+            // whole float4 inside the matrix (and, for a lower-triangular result, not right of
+            // the diagonal); ragged pieces take the scalar path below
+            whole[it] = row < p.m && c + 3 < p.n && (!p.lower_only || c + 3 <= row);
+            old[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          if (p.beta != 0.f) {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int row = row0 + it * 4 + (lane >> 3);
+              if (whole[it]) old[it] = *reinterpret_cast<const float4*>(p.c + (int64_t)row * p.ldc + c);
+            }
+          }
+#pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int rr = it * 4 + (lane >> 3), c4 = lane & 7;
             const int row = row0 + rr;
             const float4 a4 = mine[rr * 8 + (c4 ^ (rr & 7))];
             float* cp = p.c + (int64_t)row * p.ldc + c;
-            // whole float4 inside the matrix (and, for a lower-triangular result, not right of
-            // the diagonal); ragged pieces take the scalar path below
-            if (row < p.m && c + 3 < p.n && (!p.lower_only || c + 3 <= row)) {
-              float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (p.beta != 0.f) o = *reinterpret_cast<const float4*>(cp);
+            if (whole[it]) {
               *reinterpret_cast<float4*>(cp) =
-                  make_float4(fmaf(p.alpha, a4.x, p.beta * o.x), fmaf(p.alpha, a4.y, p.beta * o.y),
-                              fmaf(p.alpha, a4.z, p.beta * o.z), fmaf(p.alpha, a4.w, p.beta * o.w));
+                  make_float4(fmaf(p.alpha, a4.x, p.beta * old[it].x), fmaf(p.alpha, a4.y, p.beta * old[it].y),
+                              fmaf(p.alpha, a4.z, p.beta * old[it].z), fmaf(p.alpha, a4.w, p.beta * old[it].w));
             } else if (row < p.m && c < p.n) {
               const float o[4] = {a4.x, a4.y, a4.z, a4.w};
-  #pragma unroll
+#pragma unroll
               for (int e = 0; e < 4; ++e) {
                 if (c + e < p.n && (!p.lower_only || c + e <= row)) {
                   float val = p.alpha * o[e];
@@ -555,6 +578,7 @@ bool tgemm_launch(const TGemmArgs& g, cudaStream_t st) {
   // reductions longer than CHUNK_FROM_K are cut into chunks (see KC_SLICES): up to that length
   // the accumulator's truncation stays below 2e-6 of the result, beyond it it would keep growing
   const bool chunked = g.k > CHUNK_FROM_K;
+  p.kc_slices = g.k <= 512 ? KC_SLICES_SHORT : KC_SLICES;
   const dim3 gd(grid), bd(THREADS);
   cudaError_t e;
   if (a_from_tmem)

@@ -360,9 +360,12 @@ class DistributedGPTQuantizer:
             if owner_mode:
                 g.owner = min(range(world), key=lambda k: (load[k], k))
                 load[g.owner] += costs[i]
+                g.mine = g.owner == rank
             else:
-                g.owner = rank
-            g.mine = g.owner == rank
+                # the reference's flow (coordinator.py:224-233): every rank receives the whole
+                # Hessian and quantizes, then rank 0's result is what all ranks keep
+                g.owner = 0
+                g.mine = True
         n_global = self._n_global
         if world > 1:
             for g in groups:    # same order on every rank
@@ -708,8 +711,7 @@ class DistributedGPTQuantizer:
         groups = self._groups_of(names, quantizers)
         load = [0.0] * dc.world_size
         self._dispatch(groups, load)
-        owner_mode = dc.hessian_exchange == "owner" and dc.world_size > 1
-        shared = self._share_block(groups) if owner_mode else None
+        shared = self._share_block(groups) if dc.world_size > 1 else None
         self._report(names, self._finalize(names, layers, groups, shared))
         self._pool.join()
 
@@ -727,7 +729,7 @@ class DistributedGPTQuantizer:
                 per_block[int(head)][n] = layer
             else:
                 outside[n] = layer
-        owner_mode = dc.hessian_exchange == "owner" and dc.world_size > 1
+        share = dc.world_size > 1           # results travel between ranks in both exchange modes
         load = [0.0] * dc.world_size
         sequential = cfg.true_sequential
         ckpt = Path(cfg.checkpoint_dir) if cfg.checkpoint_dir else None
@@ -764,7 +766,7 @@ class DistributedGPTQuantizer:
             self._check_grouping(list(outside))
             og = self._groups_of(list(outside), outside_q)
             self._dispatch(og, load)
-            pending_outside = (list(outside), og, self._share_block(og) if owner_mode else None)
+            pending_outside = (list(outside), og, self._share_block(og) if share else None)
         else:
             pending_outside = None
 
@@ -808,7 +810,7 @@ class DistributedGPTQuantizer:
                     self._check_grouping(names_b)
                 groups = self._groups_of(names_b, quantizers)
                 self._dispatch(groups, load)
-                shared = self._share_block(groups) if owner_mode else None
+                shared = self._share_block(groups) if share else None
                 lag.append((b, names_b, targets, groups, shared, shard))
             if sequential and targets:
                 # the next block must see this block's quantized weights: collect now, re-run
@@ -832,7 +834,7 @@ class DistributedGPTQuantizer:
             self._check_grouping(names_o)
             og = self._groups_of(names_o, oq)
             self._dispatch(og, load)
-            sh = self._share_block(og) if owner_mode else None
+            sh = self._share_block(og) if share else None
             self._report(names_o, self._finalize(names_o, outside, og, sh))
         if self._pool is not None:
             self._pool.join()

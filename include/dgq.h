@@ -267,8 +267,12 @@ int32_t dgq_unpack_dequant(const void* packed, const void* scales, const void* z
  * byte per code otherwise); scales/zeros (N_out, n_groups) fp16; g_idx (K) int32
  * group of every input column, or NULL for c / group_size; bias (N_out) of
  * bias_dtype or NULL; x and y of x_dtype (DGQ_F32, DGQ_F16 or DGQ_BF16).
- * Tuned for M <= 16 (bound by the packed weights' HBM traffic); larger M runs
- * in chunks of 16 rows.
+ * Up to 32 rows the call is bound by the packed weights' HBM traffic and runs in chunks of 16
+ * rows on kernels that read every weight byte once.  From 33 rows on (prefill-sized M;
+ * 4-bit codes, 16-bit activations, no g_idx, K and the group size multiples of 64) one
+ * tcgen05 kernel does the whole product: weights are dequantized into shared memory as the
+ * second operand, activations arrive by TMA, fp32 accumulation in tensor memory - the
+ * 128 x 128 x K tiling kernels/triton_kernels.py:126-183 sketches.
  */
 int32_t dgq_qlinear_forward(const void* x, int32_t x_dtype, int32_t M,
                             const uint8_t* qweight, const void* scales_f16, const void* zeros_f16,

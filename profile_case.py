@@ -61,6 +61,7 @@ def main():
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--beta", type=float, default=0.0, help="gemm: C = A B^T + beta C")
     ap.add_argument("--upper", action="store_true",
                     help="hessian: update only the part on and above the diagonal")
     a = ap.parse_args()
@@ -82,10 +83,16 @@ def main():
         m = T
         A = torch.randn(m, K, generator=g, device=dev)
         B = torch.randn(N, K, generator=g, device=dev)
-        C = torch.empty(m, N, device=dev)
-        want = A.double() @ B.double().t()
-        for t in _time(lambda: _C.gemm_f32(A, B, C, False), a.reps):
-            err = float((C.double() - want).norm() / want.norm())
+        C0 = torch.randn(m, N, generator=g, device=dev)
+        C = C0.clone()
+        want = A.double() @ B.double().t() + a.beta * C0.double()
+
+        def run():
+            C.copy_(C0)
+            _C.gemm_f32(A, B, C, False, beta=a.beta)
+        run()
+        err = float((C.double() - want).norm() / want.norm())
+        for t in _time(lambda: _C.gemm_f32(A, B, C, False, beta=a.beta), a.reps):
             print(f"gemm_f32 m={m} n={N} k={K}: {t:.3f} ms  {2.0 * m * N * K / t / 1e9:.1f} TFLOP/s "
                   f"fp32-equivalent  rel. error vs fp64 {err:.2e}")
     elif a.case in ("inv_chol", "quantize"):
@@ -149,7 +156,8 @@ def main():
                                              ng, 4, 128, P(y), None)
         for t in _time_raw(call, a.reps):
             nbytes = N * K / 2 + 4 * N * ng + 2 * a.M * (K + N)
-            print(f"qlinear M={a.M} N={N} K={K}: {t * 1e3:.1f} us  {nbytes / t / 1e6:.1f} GB/s")
+            print(f"qlinear M={a.M} N={N} K={K}: {t * 1e3:.1f} us  {nbytes / t / 1e6:.1f} GB/s  "
+                  f"{2.0 * a.M * N * K / t / 1e9:.1f} TFLOP/s")
 
 
 if __name__ == "__main__":

@@ -137,7 +137,13 @@ def test_two_ranks_block_by_block(dgq, tmp_path, kind, mode):
             continue
         a, b = res[0]["state"][name].float(), b.float()
         far = ((a - b).abs() > 1e-4 * float(b.abs().max())).float().mean()
-        assert float(far) < 0.03, (name, float(far))
+        # True-sequential: a code that differs in one block changes the inputs of every later
+        # block, so only the first block is comparable weight by weight; the later ones must
+        # still be quantizations of the same quality (checked through the error sums below).
+        if kind != "decoder-sequential" or name.startswith("layers.0."):
+            assert float(far) < 0.03, (name, float(far))
+    for n, e in single.quantization_errors.items():
+        assert abs(res[0]["errors"][n] - e) <= 0.1 * e + 1e-9, n
 
 
 def test_two_devices_in_one_process(dgq):

@@ -97,3 +97,34 @@ def test_operator_with_act_order_checkpoint(dgq, M, dtype):
     got2 = torch.ops.gptq.linear(x.cuda(), qw.clone(), s, z, odd.cuda(), b)
     tol = {torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype]
     assert float((got2.float().cpu() - want2).abs().max()) <= tol * float(want2.abs().max())
+
+
+@pytest.mark.parametrize("M", [33, 64, 200, 256, 1000])
+@pytest.mark.parametrize("N_out,K,g", [(256, 512, 128), (1000, 2048, 128), (320, 1024, 64),
+                                       (128, 256, -1), (136, 4096, 256)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_qlinear_many_rows(dgq, M, N_out, K, g, dtype):
+    """More than 32 rows of activations: the tcgen05 kernel that dequantizes the weights into
+    shared memory (one rounding of (code - zero) * scale to the activation type, exact
+    products, fp32 accumulation), against dequantize + matmul (models/layers.py:155-157)."""
+    gen = torch.Generator().manual_seed(M + N_out + K)
+    codes = torch.randint(0, 16, (N_out, K), generator=gen).to(torch.uint8)
+    ng = O.n_groups(K, g)
+    scales = (torch.rand(N_out, ng, generator=gen) * 0.02 + 0.001).half()
+    zeros = torch.randint(0, 16, (N_out, ng), generator=gen).half()
+    bias = torch.randn(N_out, generator=gen).to(dtype)
+    x = torch.randn(M, K, generator=gen).to(dtype)
+    qw = O.pack_f2(codes, 4)
+    want = O.qlinear_forward(x, codes, scales, zeros, None, bias, g)
+    n0 = dgq.launch_count()
+    got = dgq.qlinear_forward(x.cuda(), qw.cuda(), scales.cuda(), zeros.cuda(), None, bias.cuda(), K, 4, g)
+    assert dgq.launch_count() == n0 + 1            # one launch for all rows
+    assert got.dtype == dtype and tuple(got.shape) == (M, N_out)
+    tol = {torch.float16: 8e-4, torch.bfloat16: 6e-3}[dtype]
+    assert float((got.float().cpu() - want).abs().max()) <= tol * float(want.abs().max())
+    # without bias, and checked against the product with the weights rounded as the kernel rounds them
+    got2 = dgq.qlinear_forward(x.cuda(), qw.cuda(), scales.cuda(), zeros.cuda(), None, None, K, 4, g)
+    Wt = O.dequant(codes, scales, zeros, None, g).to(dtype).double()
+    exact = (x.double() @ Wt.t())
+    out_eps = {torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8}[dtype]
+    assert float((got2.double().cpu() - exact).abs().max()) <= 1.01 * out_eps * float(exact.abs().max()) + 1e-6

@@ -227,3 +227,30 @@ def test_actorder_rank_with_non_finite_diagonal(dgq):
     assert torch.equal(perm.cpu().long(), want)
     assert torch.equal(torch.sort(perm.cpu()).values.long(), torch.arange(K))
     assert torch.equal(inv.cpu().long()[want], torch.arange(K))
+
+
+def test_repeated_runs_are_bit_identical(dgq):
+    """The whole chain (act-order, preparation, inverse factor with its side streams, block
+    quantization with early-launched kernels) gives the same bits every time it is given the
+    same Hessian and weights; small shapes, where every kernel of the chain is short and the
+    launches overlap the most."""
+    from distributed_gptq_b200 import GPTQ
+    W, X = synth_layer(384, 256, 2048, 77)
+    X[:, 5] = 0                      # a dead column as well
+    seed = GPTQ(nn.Linear(256, 384, bias=False).cuda(), bits=4)
+    seed.add_batch(X.reshape(4, -1, 256).cuda(), None)
+    H = seed.H.clone()
+    first = None
+    for rep in range(10):
+        lin = nn.Linear(256, 384, bias=False)
+        lin.weight.data = W.clone()
+        lin = lin.cuda()
+        q = GPTQ(lin, bits=4, group_size=128, actorder=True)
+        q.H = H
+        q.nsamples = 4
+        q.quantize()
+        got = (q.codes.clone(), q.scale.clone(), q.zero.clone(), lin.weight.data.clone())
+        if first is None:
+            first = got
+        for a, b in zip(first, got):
+            assert torch.equal(a, b), rep
