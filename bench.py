@@ -853,7 +853,9 @@ def main():
                     "prepare_permute": round(lib.get("prepare", 0.0) + lib.get("permute", 0.0), 4),
                     "inverse": lib.get("inv_chol"), "quantize": lib.get("gptq_quantize"),
                     "pack": lib.get("pack"), "share_broadcast": per.get("share_s", 0.0),
-                    "host_waiting_for_chains": per.get("host_wait_s", 0.0)},
+                    "host_waiting_for_chains": per.get("host_wait_s", 0.0),
+                    "host_enqueueing_forward": per.get("host_enqueue_forward_s"),
+                    "host_enqueueing_chains": per.get("host_enqueue_chains_s")},
                 "note": "rank 0; forward is measured on the main stream, the chain phases on side "
                         "streams that run beside it, collectives from issue to completion",
                 "hessian_tflops_executed": achieved,

@@ -13,8 +13,12 @@
 //      general variant for ragged blocks and groups narrower than 32 columns.)
 //   2. trailing update - W[:, i2:] -= Err * U[i1:i2, i2:], an fp32-accurate product on
 //      the tensor cores (tgemm.cu; on the CUDA cores for ragged or tiny shapes), applied
-//      in two levels: at once to the rest of the current 512-column super-block, and once
-//      per super-block (reduction length 512) to all columns beyond it.
+//      in two levels: at once to the rest of the current 256-column super-block, and once
+//      per super-block (reduction length 256) to all columns beyond it.  (512 columns moved
+//      less data, but the tensor core's accumulator truncates and the error of a 512-deep
+//      update, whose terms cancel to a result far smaller than their magnitudes, showed as
+//      code mismatches at K = 11008; cutting that product into two chunks cost more time than
+//      the narrower window.)
 //
 // Group scale/zero are taken from W as it stands when the group's first column is
 // reached by the block loop (all earlier blocks' trailing updates applied, none of
@@ -29,7 +33,7 @@
 namespace {
 
 constexpr int MAX_BLOCK = 128;
-constexpr int SUPER_BLOCK = 512;   // columns whose updates of far columns are applied together
+constexpr int SUPER_BLOCK = 256;   // columns whose updates of far columns are applied together
 constexpr int ROWS_PER_CTA = 16;  // one warp each
 
 struct QuantArgs {

@@ -504,6 +504,10 @@ class DistributedGPTQuantizer:
         e.record()
         return e
 
+    def _host(self, key: str, t0: float) -> None:
+        """Adds the host time since t0 (perf_counter) to timings[key]."""
+        self.timings[key] = self.timings.get(key, 0.0) + time.perf_counter() - t0
+
     def _span(self, key: str, start, work=None) -> None:
         """Adds (now - start) on the current stream to timings[key]; with `work`, the span is
         measured on a stream of its own that waits for the collective."""
@@ -785,6 +789,7 @@ class DistributedGPTQuantizer:
             handles = self._hook_layers(targets, quantizers, bstate) if resumed is None else []
             nxt = []
             t0 = self._mark()
+            h0 = time.perf_counter()
             try:
                 for i, h in enumerate(hidden):
                     out = self._block_call(block, h, captured[i][0], captured[i][1])
@@ -796,6 +801,7 @@ class DistributedGPTQuantizer:
                 for hd in handles:
                     hd.remove()
             self._span("forward_s", t0)
+            self._host("host_enqueue_forward_s", h0)
             if resumed is not None:
                 if not sequential:  # one-shot: every block sees the unquantized model's activations
                     io.apply_block_weights(targets, resumed)
@@ -808,9 +814,11 @@ class DistributedGPTQuantizer:
                 self._leader.update({n: bstate["leader"].get(n, n) for n in names_b})
                 if b == 0:
                     self._check_grouping(names_b)
+                h0 = time.perf_counter()
                 groups = self._groups_of(names_b, quantizers)
                 self._dispatch(groups, load)
                 shared = self._share_block(groups) if share else None
+                self._host("host_enqueue_chains_s", h0)
                 lag.append((b, names_b, targets, groups, shared, shard))
             if sequential and targets:
                 # the next block must see this block's quantized weights: collect now, re-run

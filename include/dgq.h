@@ -171,8 +171,8 @@ int32_t dgq_gemm_f32(const float* a, int64_t lda, const float* b, int64_t ldb, i
  * receives sum(((w - w_hat)/d)^2) (core/gptq.py:183,191); it is overwritten.
  * blocksize must be 128 or less and group_size, when it is smaller than K, must
  * either divide blocksize or be a multiple of it.  The workspace holds scaled errors:
- * dgq_gptq_quantize_workspace_bytes() asks for N_out x 512 floats (updates of far columns
- * are then batched over 512 columns); any size down to N_out x 128 floats is accepted.
+ * dgq_gptq_quantize_workspace_bytes() asks for N_out x 256 floats (updates of far columns
+ * are then batched over 256 columns); any size down to N_out x 128 floats is accepted.
  */
 int64_t dgq_gptq_quantize_workspace_bytes(int32_t N_out, int32_t K, int32_t blocksize);
 int32_t dgq_gptq_quantize(float* W, int64_t ldw, const float* U, int64_t ldu,

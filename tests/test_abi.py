@@ -41,7 +41,7 @@ def test_host_only_entry_points():
     assert L.dgq_packed_row_bytes(7, 4, _C.FMT_BYTES_HI_FIRST) < 0   # odd column count
     assert L.dgq_packed_row_bytes(8, 5, _C.FMT_BYTES_HI_FIRST) < 0   # bad bit width
     assert L.dgq_inv_chol_workspace_bytes(4096) > 0
-    assert L.dgq_gptq_quantize_workspace_bytes(4096, 4096, 128) == 4096 * 512 * 4
+    assert L.dgq_gptq_quantize_workspace_bytes(4096, 4096, 128) == 4096 * 256 * 4
     assert L.dgq_gptq_quantize_workspace_bytes(4096, 4096, 256) < 0
 
 

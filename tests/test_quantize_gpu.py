@@ -177,8 +177,8 @@ def test_fast_block_kernel_against_general_kernel(dgq):
 
 # ---- groups wider than a block and the width of the deferred-update window ------------------
 @pytest.mark.parametrize("K,g,ws_cols", [
-    (1536, 256, 384),     # a caller-sized workspace of 384 columns: groups would straddle it
-    (1536, 384, None),    # default workspace (512 columns), group 384
+    (1536, 256, 384),     # a caller-sized workspace of 384 columns
+    (1536, 384, None),    # default workspace (256 columns): a group of 384 would straddle windows
     (2048, 1024, None),   # a group wider than the window
     (1280, 640, None),
 ])

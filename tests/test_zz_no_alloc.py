@@ -42,8 +42,8 @@ def _call_noalloc(dgq, W, U, bits, group_size, blocksize):
 
 
 # The last two cases sit at the edges of the fixed scratch: 16384 rows leave room for one
-# 128-column block of scaled errors only, and 5120 rows for three (groups of 256 columns must
-# then not straddle the window in which far columns' updates are deferred).
+# 128-column block of scaled errors only; 5120 rows with groups of 256 columns exercise a
+# group wider than a block inside the window in which far columns' updates are deferred.
 @pytest.mark.parametrize("N_out,K,bits,g", [(300, 512, 4, 128), (64, 384, 3, 64),
                                             (16384, 256, 4, 128), (5120, 1024, 4, 256)])
 def test_noalloc_matches_workspace_entry_point_twice(dgq, N_out, K, bits, g):
