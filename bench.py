@@ -135,7 +135,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one hessian_syrk_kernel launch from ncu
 # captures on small cases (profiles/hessian_syrk_kernel.md): (K, T) -> bytes
-HESS_TRAFFIC_CAPTURES = {4096: (32768, 347.7e6), 11008: (16384, 2.698e9)}
+HESS_TRAFFIC_CAPTURES = {4096: (65536, 575.5e6), 11008: (32768, 4.148e9)}
 
 
 def hessian_traffic(K: int, T: int) -> float:
@@ -367,13 +367,16 @@ def assign_owners(world: int):
 
 class Sweep:
     """The standalone layer sweep: 12 independent GPTQ runs per step, each with its own
-    Hessian accumulation; at N > 1 the runs are processed heaviest input width first and a
-    run's chain starts on its owner as soon as its Hessian has been reduced, while the
-    remaining Hessians are still being accumulated."""
+    Hessian accumulation.  At N > 1 all Hessians are accumulated and reduced first and the
+    owners' chains follow (`chains="after"`); starting a run's chain right after its reduce
+    (`"during"`) was measured slower at every N (8 GPUs: 76 ms against 41 ms per sweep): the
+    chains of the widest layers are the critical path, and their hundreds of short dependent
+    kernels each wait for a free SM while Hessian kernels fill the GPU."""
 
-    def __init__(self, rank: int, world: int, device):
+    def __init__(self, rank: int, world: int, device, chains: str = "after"):
         from distributed_gptq_b200 import _C  # noqa: F401  (fails loudly without the library)
         self.rank, self.world, self.device = rank, world, device
+        self.chains = chains     # several GPUs: chains "during" the Hessian phase or "after" it
         self.runs, self.owner = assign_owners(world)
         self.my_seqs = list(range(rank, NSEQ, world))
         self.W = [make_weights(i, n, k, device) for i, (_, n, k) in enumerate(LAYERS)]
@@ -472,11 +475,11 @@ class Sweep:
                     staged.append(chunks)
         pending, jobs, results = [], [], []
         pool = self.pool
-        # Several GPUs: the runs with the widest input (the longest chains, K = 11008) go first,
-        # and every run's chain is enqueued right after its reduce, so that the long chains run
-        # on their owners' side streams while the other Hessians are still being accumulated.
+        # `chains="during"`: the runs with the widest input (the longest chains, K = 11008) go
+        # first and every run's chain is enqueued right after its reduce.
         order = list(range(len(self.runs)))
-        if self.world > 1:
+        overlap = self.world > 1 and self.chains == "during"
+        if overlap:
             order.sort(key=lambda ri: -run_cost(LAYERS[self.runs[ri][0]][1], LAYERS[self.runs[ri][0]][2]))
         for ri in order:
             li, bits, act = self.runs[ri]
@@ -502,7 +505,7 @@ class Sweep:
             # and power cap); chains enqueued beside them only slowed both down, so they follow
             # in phase B.  Host inputs (the accumulation waits for PCIe) or several GPUs (most
             # ranks do not own the run): the chain is enqueued at once.
-            if self.world > 1 or from_host:
+            if overlap or (self.world == 1 and from_host):
                 jobs.append(self._launch(pending.pop(0), from_host, pool))
         pending.sort(key=lambda it: -run_cost(LAYERS[self.runs[it[0]][0]][1],
                                               LAYERS[self.runs[it[0]][0]][2]))
@@ -660,6 +663,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="debugging: fewer decoder blocks than the named model (flagged in config)")
     ap.add_argument("--true-sequential", action="store_true")
+    ap.add_argument("--sweep-chains", default="after", choices=["during", "after"],
+                    help="sweep on several GPUs: enqueue a run's chain after all Hessians (default) or "
+                         "right after its reduce, beside the remaining Hessian kernels (measured slower: "
+                         "the chains are on the critical path and run 3x slower on a busy GPU)")
     ap.add_argument("--cpu-outright", action="store_true",
                     help="reference arm: time the whole workload on the CPU (small models only)")
     ap.add_argument("--linear-check", action="store_true",
@@ -758,7 +765,7 @@ def main():
                            true_sequential=args.true_sequential)
         step_dev, step_host = (lambda: wl.step(False)), (lambda: wl.step(True))
     else:
-        wl = Sweep(rank, world, device)
+        wl = Sweep(rank, world, device, args.sweep_chains)
         wl.load_device_inputs()
         step_dev, step_host = (lambda: wl.step(False)), (lambda: wl.step(True))
     print(f"[bench] rank {rank}: workload built in {time.time() - t_build:.1f} s", file=sys.stderr,
@@ -833,8 +840,8 @@ def main():
             "launches": n_calls, "avg_launch_ms": hess_ms / n_calls if n_calls else None,
             "tokens_per_launch": tokens_per_call,
             "traffic": traffic,
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of small-case captures "
-                              "(K=4096/T=32768: 347.7 MB, K=11008/T=16384: 2.698 GB), scaled by the "
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of single-launch captures "
+                              "(K=4096/T=65536: 575.5 MB, K=11008/T=32768: 4.148 GB), scaled by the "
                               "tokens per launch and averaged over the launch shapes of a step"
             if traffic else None,
             "kernels_by_time": kernels,
@@ -855,7 +862,13 @@ def main():
                     "pack": lib.get("pack"), "share_broadcast": per.get("share_s", 0.0),
                     "host_waiting_for_chains": per.get("host_wait_s", 0.0),
                     "host_enqueueing_forward": per.get("host_enqueue_forward_s"),
-                    "host_enqueueing_chains": per.get("host_enqueue_chains_s")},
+                    "host_enqueueing_chains": per.get("host_enqueue_chains_s"),
+                    "host_setup": per.get("host_setup_s"),
+                    "host_capture_of_first_block_inputs": per.get("host_capture_s"),
+                    "host_replay_check": per.get("host_replay_check_s"),
+                    "host_collecting_last_blocks": per.get("host_tail_collect_s"),
+                    "host_final_sync": per.get("host_final_sync_s"),
+                    "quantize_model_total": per.get("total_s")},
                 "note": "rank 0; forward is measured on the main stream, the chain phases on side "
                         "streams that run beside it, collectives from issue to completion",
                 "hessian_tflops_executed": achieved,

@@ -8,13 +8,14 @@
 // form in global memory: a CTA works on a 128-row x 128-feature tile of y and walks K in
 // slices of 64 columns; per slice
 //   - warp 0 fetches the 128 x 64 slice of x with one TMA box (128-byte swizzle): operand A;
-//   - warps 2-5 ("converters", one thread per output feature) read the feature's 32 bytes of
-//     packed codes straight from global memory (prefetched one slice ahead), turn them into
-//     64 values (code - zero) * scale of the activation type and store them as the feature's
-//     128-byte row of operand B, in the same swizzled layout a TMA box would have produced;
+//   - warps 2-9 ("converters", two threads per output feature) read the feature's 32 bytes of
+//     packed codes straight from global memory (16 bytes per thread, four slices ahead: a load
+//     takes longer than a slice), turn them into 64 values (code - zero) * scale of the
+//     activation type and store them as the feature's 128-byte row of operand B, in the same
+//     swizzled layout a TMA box would have produced;
 //   - warp 1 issues four tcgen05.mma kind::f16 (M = 128 rows, N = 128 features, K = 16) into
 //     a 128-column fp32 accumulator in tensor memory;
-// and warps 6-9 drain finished accumulators (two alternate), add the bias, round and store.
+// and warps 10-13 drain finished accumulators (two alternate), add the bias, round and store.
 // CTAs are persistent; tiles are ordered with the row tile running fastest, so the CTAs
 // running at one time share packed weights through L2.
 //
@@ -35,7 +36,8 @@ constexpr int TILE_M = 128, TILE_N = 128, BK = 64;
 constexpr int A_BYTES = TILE_M * BK * 2, B_BYTES = TILE_N * BK * 2;     // 16 KB each
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STAGES = 4;
-constexpr int THREADS = 320;
+constexpr int CONV_WARPS = 8;
+constexpr int THREADS = 32 * (2 + CONV_WARPS + 4);
 constexpr uint32_t TMEM_COLS = 256;
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
 
@@ -51,19 +53,42 @@ struct Params {
   int tiles_m, tiles_n, n_tiles, n_slices;
 };
 
+// Per activation type: packing of two floats, and the arithmetic of the short dequantization.
+// A 4-bit code c OR-ed into the mantissa of BASE (1024 in fp16, 128 in bf16) is the number
+// BASE + c; subtracting BASE + zero is exact for an integer zero point, and one multiplication
+// by the scale rounds once - the same value as rounding (c - zero) * scale computed in fp32.
 template <typename T> struct Cvt;
 template <> struct Cvt<__half> {
   static constexpr uint32_t FMT = tc05::FMT_F16;
+  static constexpr uint32_t MAGIC = 0x64006400u;
+  static constexpr float BASE = 1024.f;
   static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
   }
+  // (BASE + c) - (BASE + zero) is exact, the scale is an fp16 number: one rounding
+  static __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint32_t sub, uint32_t mul, float) {
+    const __half2 r = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&v),
+                                      *reinterpret_cast<const __half2*>(&sub)),
+                              *reinterpret_cast<const __half2*>(&mul));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
 };
 template <> struct Cvt<__nv_bfloat16> {
   static constexpr uint32_t FMT = tc05::FMT_BF16;
+  static constexpr uint32_t MAGIC = 0x43004300u;
+  static constexpr float BASE = 128.f;
   static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  // (BASE + c) - (BASE + zero) is exact in bf16, but the fp16 scale is not a bf16 number: the
+  // difference is widened to fp32 (a shift), multiplied there and rounded once
+  static __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint32_t sub, uint32_t, float sc) {
+    const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&sub));
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(&d);
+    return pack2(__uint_as_float(u << 16) * sc, __uint_as_float(u & 0xFFFF0000u) * sc);
   }
 };
 
@@ -87,7 +112,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       tc05::mbar_init(&ctl->full[s], 1);
-      tc05::mbar_init(&ctl->conv[s], 4);
+      tc05::mbar_init(&ctl->conv[s], CONV_WARPS);
       tc05::mbar_init(&ctl->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -167,58 +192,86 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
+  } else if (warp < 2 + CONV_WARPS) {
     // ------------------------------------------------------------------ converters (weights)
-    const int f = threadIdx.x - 64;                  // feature row of the tile, 0..127
+    const int ct = threadIdx.x - 64;                 // 0..255
+    const int f = ct & (TILE_N - 1);                 // feature row of the tile
+    const int half = ct >> 7;                        // which 16 of the slice's 32 bytes of codes
     const int slices_per_group = a.n_groups == 1 ? p.n_slices : a.group_size / BK;
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       const int tn = t / p.tiles_m;
       const int n = min(tn * TILE_N + f, a.N_out - 1);       // rows past the end repeat the last
-      const uint8_t* wrow = a.qw + (int64_t)n * a.row_bytes;
+      const uint8_t* wrow = a.qw + (int64_t)n * a.row_bytes + half * 16;
       const __half* srow = a.scales + (int64_t)n * a.n_groups;
       const __half* zrow = a.zeros + (int64_t)n * a.n_groups;
-      uint4 c0 = *reinterpret_cast<const uint4*>(wrow);      // slice 0: columns 0..63 = 32 bytes
-      uint4 c1 = *reinterpret_cast<const uint4*>(wrow + 16);
+      auto fetch = [&](int sl) -> uint4 {
+        return sl < p.n_slices ? *reinterpret_cast<const uint4*>(wrow + (int64_t)sl * 32)
+                               : make_uint4(0u, 0u, 0u, 0u);
+      };
+      uint4 q0 = fetch(0), q1 = fetch(1), q2 = fetch(2), q3 = fetch(3);
       float sc = 0.f, zs = 0.f;
-      for (int s_ = 0; s_ < p.n_slices; ++s_, ++it) {
+      uint32_t sub2 = 0u, mul2 = 0u;       // (BASE + zero, BASE + zero) and (scale, scale) as pairs of T
+      bool short_path = false;
+      // one slice: this thread's 16 bytes of codes -> 32 values -> four 16-byte pieces of row f
+      auto step = [&](int sl, const uint4& codes) -> bool {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        if (s_ % slices_per_group == 0) {
-          const int g = s_ / slices_per_group;
+        ++it;
+        if (sl % slices_per_group == 0) {
+          const int g = sl / slices_per_group;
           sc = __half2float(srow[g]);
-          zs = __half2float(zrow[g]) * sc;                   // w = code * scale - zero * scale
-        }
-        const uint4 cur0 = c0, cur1 = c1;
-        if (s_ + 1 < p.n_slices) {                           // next slice's codes, in flight
-          c0 = *reinterpret_cast<const uint4*>(wrow + (s_ + 1) * 32);
-          c1 = *reinterpret_cast<const uint4*>(wrow + (s_ + 1) * 32 + 16);
+          const float z = __half2float(zrow[g]);
+          zs = z * sc;                                       // w = code * scale - zero * scale
+          // integer zero points (every GPTQ zero is one) take the short path
+          short_path = (z == rintf(z)) && fabsf(z) <= 64.f;
+          sub2 = Cvt<T>::pack2(Cvt<T>::BASE + z, Cvt<T>::BASE + z);
+          mul2 = Cvt<T>::pack2(sc, sc);
         }
         const bool got = tc05::mbar_wait_bounded(&ctl->empty[s], ph ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0 && a.info) { a.info[0] = DGQ_INFO_WAIT_TIMEOUT; a.info[1] = 24; }
-          ok = false;
-          break;
+          return false;
         }
         // row f of operand B: eight 16-byte pieces, piece c stored at position c ^ (f % 8)
         uint4* brow = reinterpret_cast<uint4*>(stages + (size_t)s * STAGE_BYTES + A_BYTES) + f * 8;
-        const uint32_t words[8] = {cur0.x, cur0.y, cur0.z, cur0.w, cur1.x, cur1.y, cur1.z, cur1.w};
+        const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+        const bool fast = __all_sync(0xffffffffu, short_path);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          // one 32-bit word = 4 bytes = 8 codes = columns 8c .. 8c+7 of the slice
-          const uint32_t w = words[c];
+        for (int c = 0; c < 4; ++c) {
+          // one 32-bit word = 4 bytes = 8 codes = columns 8 (4 half + c) .. + 7 of the slice
+          const uint32_t w = words[c], w4 = w >> 4;
           uint32_t o[4];
+          if (fast) {
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            const float lo = (float)((w >> (8 * b)) & 15u), hi = (float)((w >> (8 * b + 4)) & 15u);
-            o[b] = Cvt<T>::pack2(fmaf(lo, sc, -zs), fmaf(hi, sc, -zs));
+            for (int b = 0; b < 4; ++b) {
+              // byte b of w (low nibble = even column) and of w >> 4 (low nibble = odd column)
+              const uint32_t pr = __byte_perm(w, w4, ((4 + b) << 8) | b);
+              o[b] = Cvt<T>::dequant_pair((pr & 0x000F000Fu) | Cvt<T>::MAGIC, sub2, mul2, sc);
+            }
+          } else {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const float lo = (float)((w >> (8 * b)) & 15u), hi = (float)((w >> (8 * b + 4)) & 15u);
+              o[b] = Cvt<T>::pack2(fmaf(lo, sc, -zs), fmaf(hi, sc, -zs));
+            }
           }
-          brow[c ^ (f & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
+          brow[(4 * half + c) ^ (f & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
         }
         // make the generic-proxy writes visible to the tensor core's (async proxy) reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) tc05::mbar_arrive(&ctl->conv[s]);
+        return true;
+      };
+      for (int s_ = 0; s_ < p.n_slices && ok; s_ += 4) {
+        // four slices per turn so that the four code registers have fixed names; each is
+        // refilled, for the slice four ahead, as soon as it has been used
+        ok = step(s_, q0);
+        q0 = fetch(s_ + 4);
+        if (ok && s_ + 1 < p.n_slices) { ok = step(s_ + 1, q1); q1 = fetch(s_ + 5); }
+        if (ok && s_ + 2 < p.n_slices) { ok = step(s_ + 2, q2); q2 = fetch(s_ + 6); }
+        if (ok && s_ + 3 < p.n_slices) { ok = step(s_ + 3, q3); q3 = fetch(s_ + 7); }
       }
     }
   } else {

@@ -191,6 +191,7 @@ class DistributedGPTQuantizer:
         self.profile = False
         self._pool: Optional[ChainPool] = None
         self._share_stream: Optional[torch.cuda.Stream] = None
+        self._xchg_stream: Optional[torch.cuda.Stream] = None
         self.hessians: Dict[str, torch.Tensor] = {}
         self._leader: Dict[str, str] = {}
         self.mode_used: Optional[str] = None
@@ -292,31 +293,30 @@ class DistributedGPTQuantizer:
     @torch.no_grad()
     def _capture_block_inputs(self, model: nn.Module, blocks: nn.ModuleList, batches: List,
                               outside: Dict[str, nn.Module], outside_q: Dict[str, GPTQ],
-                              state: dict, stop_early: bool):
+                              state: dict, stop_early: bool, probe: bool = False):
         """Runs the model on every batch up to its first block and records what the block is
-        called with.  On the first batch the pass goes on to the second block, whose input is
-        kept to check the replay.  Layers outside the blocks are calibrated here when the pass
-        may not stop early."""
+        called with.  With ``probe`` the pass goes on to the second block, whose input is
+        returned too (to check the replay of the first block), and stops there.  Layers outside
+        the blocks are calibrated here when the pass may not stop early."""
         captured: List[Tuple[tuple, dict]] = []
-        probe: Dict[str, torch.Tensor] = {}
-        want_probe = {"on": True}
+        seen_h1: Dict[str, torch.Tensor] = {}
 
         def first_hook(module, args, kwargs):
             captured.append((tuple(a.detach() if torch.is_tensor(a) else a for a in args),
                              dict(kwargs)))
-            if stop_early and not want_probe["on"]:
+            if stop_early and not probe:
                 raise _StopForward()
 
         def second_hook(module, args, kwargs):
-            if want_probe["on"]:
-                h = args[0] if args else kwargs.get("hidden_states")
-                probe["h1"] = h.detach()
-                if stop_early:
-                    raise _StopForward()
+            h = args[0] if args else kwargs.get("hidden_states")
+            seen_h1["h1"] = h.detach()
+            raise _StopForward()
 
-        handles = [blocks[0].register_forward_pre_hook(first_hook, with_kwargs=True),
-                   blocks[1].register_forward_pre_hook(second_hook, with_kwargs=True)]
-        handles += self._hook_layers(outside, outside_q, state) if not stop_early else []
+        handles = [blocks[0].register_forward_pre_hook(first_hook, with_kwargs=True)]
+        if probe:
+            handles.append(blocks[1].register_forward_pre_hook(second_hook, with_kwargs=True))
+        elif not stop_early:
+            handles += self._hook_layers(outside, outside_q, state)
         extra = self._forward_extras(model)
         try:
             for batch in batches:
@@ -324,13 +324,13 @@ class DistributedGPTQuantizer:
                     self._run_model(model, batch, extra)
                 except _StopForward:
                     pass
-                want_probe["on"] = False
-                state.setdefault("seen", []).clear()
-                state["first"] = False
+                if not probe:
+                    state.setdefault("seen", []).clear()
+                    state["first"] = False
         finally:
             for h in handles:
                 h.remove()
-        return captured, probe.get("h1")
+        return captured, seen_h1.get("h1")
 
     @staticmethod
     def _block_call(block: nn.Module, h: torch.Tensor, args: tuple, kwargs: dict) -> torch.Tensor:
@@ -347,9 +347,12 @@ class DistributedGPTQuantizer:
         return out[0] if isinstance(out, (tuple, list)) else out
 
     # ------------------------------------------------------------------ exchange, chains, sharing
-    def _dispatch(self, groups: List[_Group], load: List[float]) -> None:
+    def _dispatch(self, groups: List[_Group], load: List[float],
+                  after: Optional[torch.cuda.Event] = None) -> None:
         """Places the groups on ranks (greedy on the cumulative load, heaviest first), starts
-        the reduction of their Hessians and enqueues the owners' chains on the side streams."""
+        the reduction of their Hessians and enqueues the owners' chains on the side streams.
+        ``after``: the event that marks the Hessians complete on the main stream; without it
+        everything queued on the main stream so far is waited for."""
         cfg, co, dc = self.quant_config, self.coordinator, self.dist_config
         world, rank = dc.world_size, dc.rank
         owner_mode = dc.hessian_exchange == "owner" and world > 1
@@ -368,18 +371,32 @@ class DistributedGPTQuantizer:
                 g.mine = True
         n_global = self._n_global
         if world > 1:
+            # The collectives are issued from a stream of their own that waits for `after` only:
+            # issued from the main stream they would also wait for whatever has been queued
+            # there since (the next block's pass).
+            main = torch.cuda.current_stream(co.device)
+            if self._xchg_stream is None:
+                self._xchg_stream = torch.cuda.Stream(device=co.device)
+            xs = self._xchg_stream
+            if after is not None:
+                xs.wait_event(after)
+            else:
+                xs.wait_stream(main)
             for g in groups:    # same order on every rank
                 lead = g.q[0]
                 if lead._Hbuf is None:   # this rank saw no sample: it still takes part
                     K8 = (lead.columns + 7) // 8 * 8
-                    lead._Hbuf = torch.zeros((K8, K8), dtype=torch.float32, device=co.device)
-                t0 = self._mark()
-                if owner_mode:
-                    g.reduce_work = co.comm.reduce_tensor(lead._Hbuf, dst=g.owner, async_op=True)
-                else:
-                    g.reduce_work = co.comm.all_reduce_tensor(lead._Hbuf, async_op=True)
+                    with torch.cuda.stream(xs):
+                        lead._Hbuf = torch.zeros((K8, K8), dtype=torch.float32, device=co.device)
+                lead._Hbuf.record_stream(xs)
+                with torch.cuda.stream(xs):
+                    t0 = self._mark()
+                    if owner_mode:
+                        g.reduce_work = co.comm.reduce_tensor(lead._Hbuf, dst=g.owner, async_op=True)
+                    else:
+                        g.reduce_work = co.comm.all_reduce_tensor(lead._Hbuf, async_op=True)
+                    self._span("exchange_s", t0, g.reduce_work)
                 lead._lower_stale = True    # the partial sums only carry the upper triangle
-                self._span("exchange_s", t0, g.reduce_work)
         if self._pool is None:      # made once: the caching allocator pools memory per stream
             self._pool = ChainPool(co.device, n_streams=4)
         fmt = io.file_format(cfg.bits)
@@ -405,7 +422,7 @@ class DistributedGPTQuantizer:
                 packed = [io.packed_state(m, q, fmt) for m, q in zip(g.members, g.q)]
                 return status, packed
 
-            g.future = self._pool.submit(chain)
+            g.future = self._pool.submit(chain, after=after)
 
     def _share_layout(self, groups: List[_Group], owner: int):
         """Pieces of the flat buffer rank ``owner`` sends for one block: for every layer it
@@ -657,6 +674,7 @@ class DistributedGPTQuantizer:
                 layers = {n: mods[n] for n in layers_to_quantize}
             logger.info("Found %d layers to quantize", len(layers))
 
+            h_setup = time.perf_counter()
             samples = calibration_samples(calibration_data, cfg.calibration_samples)
             if not samples:
                 raise ValueError("no calibration data")
@@ -674,12 +692,15 @@ class DistributedGPTQuantizer:
             self._results: Dict[str, dict] = {}
 
             plan = find_blocks(model, layers) if self.blockwise else None
+            self._host("host_setup_s", h_setup)
             done = False
             if plan is not None:
                 done = self._quantize_blockwise(model, plan, layers, batches, first_sample)
             if not done:
                 self._quantize_whole(model, layers, batches, first_sample)
+            h0 = time.perf_counter()
             torch.cuda.synchronize(co.device)
+            self._host("host_final_sync_s", h0)
 
             for n in layers:        # model order
                 self._record(n, layers[n], self._results[n])
@@ -747,22 +768,32 @@ class DistributedGPTQuantizer:
         state["accumulate"] = not discovery_only
         outside_now = bool(outside) and not sequential
         t_cal = self._mark()
-        captured, h1 = self._capture_block_inputs(model, blocks, run_batches, outside, outside_q,
-                                                  state, stop_early=not outside_now)
+        h0 = time.perf_counter()
+        # Replay check on one sequence: the model is run up to its second block, and the first
+        # block, called the way the model called it, must reproduce the second block's input.
+        probe_sample = _split_samples(run_batches[0])[0]
+        pc, h1 = self._capture_block_inputs(model, blocks, [probe_sample], {}, {}, {"first": True},
+                                            stop_early=True, probe=True)
+        ok = len(pc) == 1 and h1 is not None
+        if ok:
+            ph = pc[0][0][0] if pc[0][0] else pc[0][1].get("hidden_states")
+            out = self._block_call(blocks[0], ph, pc[0][0], pc[0][1]) if torch.is_tensor(ph) else None
+            ok = (out is not None and out.shape == h1.shape and
+                  bool(torch.allclose(out.float(), h1.float(), rtol=1e-3, atol=1e-5)))
+            del out
+        if not ok:
+            logger.warning("block-wise calibration: replaying %s[0] does not reproduce the input "
+                           "of %s[1]; using whole-model passes", list_name, list_name)
+            return False
+        self._host("host_replay_check_s", h0)
+        captured, _ = self._capture_block_inputs(model, blocks, run_batches, outside, outside_q,
+                                                 state, stop_early=not outside_now)
+        self._host("host_capture_s", h0)
         if not captured or len(captured) != len(run_batches):
             logger.warning("block-wise calibration: %s[0] was not reached once per batch; "
                            "using whole-model passes", list_name)
             return False
         hidden = [(c[0][0] if c[0] else c[1]["hidden_states"]) for c in captured]
-        # replay check: the first block, called as recorded, must reproduce the second block's input
-        if h1 is not None:
-            out = self._block_call(blocks[0], hidden[0], captured[0][0], captured[0][1])
-            ok = out.shape == h1.shape and torch.allclose(out.float(), h1.float(), rtol=1e-3, atol=1e-5)
-            del out
-            if not ok:
-                logger.warning("block-wise calibration: replaying %s[0] does not reproduce the "
-                               "input of %s[1]; using whole-model passes", list_name, list_name)
-                return False
         self.mode_used = "block-wise" + (" true-sequential" if sequential else "")
         self._span("forward_s", t_cal)
         if outside_now:
@@ -775,6 +806,26 @@ class DistributedGPTQuantizer:
             pending_outside = None
 
         lag: List[tuple] = []       # blocks whose chains are enqueued but not collected yet
+        # One-shot mode: the chains of block b are enqueued only after the pass of block b+1.
+        # A chain is a thousand and more launches on a stream that cannot start before its
+        # block's pass has run on the device, and the launch queue of a stream is finite: the
+        # host blocks in the middle of enqueueing the chain until the device gets there.  With
+        # the next pass already queued, the main stream has work for that time.
+        deferred: Optional[tuple] = None
+
+        def dispatch_deferred():
+            nonlocal deferred
+            if deferred is None:
+                return
+            b_, names_, targets_, quantizers_, shard_, ev_ = deferred
+            deferred = None
+            h0_ = time.perf_counter()
+            groups_ = self._groups_of(names_, quantizers_)
+            self._dispatch(groups_, load, after=ev_)
+            shared_ = self._share_block(groups_) if share else None
+            self._host("host_enqueue_chains_s", h0_)
+            lag.append((b_, names_, targets_, groups_, shared_, shard_))
+
         for b, block in enumerate(blocks):
             targets = per_block[b]
             names_b = list(targets)
@@ -802,6 +853,9 @@ class DistributedGPTQuantizer:
                     hd.remove()
             self._span("forward_s", t0)
             self._host("host_enqueue_forward_s", h0)
+            done_b = torch.cuda.Event()
+            done_b.record(torch.cuda.current_stream(co.device))     # this block's Hessians are complete
+            dispatch_deferred()                                     # the previous block's chains
             if resumed is not None:
                 if not sequential:  # one-shot: every block sees the unquantized model's activations
                     io.apply_block_weights(targets, resumed)
@@ -814,12 +868,9 @@ class DistributedGPTQuantizer:
                 self._leader.update({n: bstate["leader"].get(n, n) for n in names_b})
                 if b == 0:
                     self._check_grouping(names_b)
-                h0 = time.perf_counter()
-                groups = self._groups_of(names_b, quantizers)
-                self._dispatch(groups, load)
-                shared = self._share_block(groups) if share else None
-                self._host("host_enqueue_chains_s", h0)
-                lag.append((b, names_b, targets, groups, shared, shard))
+                deferred = (b, names_b, targets, quantizers, shard, done_b)
+                if sequential:
+                    dispatch_deferred()
             if sequential and targets:
                 # the next block must see this block's quantized weights: collect now, re-run
                 self._collect(lag.pop())
@@ -830,8 +881,11 @@ class DistributedGPTQuantizer:
             elif len(lag) > 2:
                 self._collect(lag.pop(0))    # bounds how far the host runs ahead of the device
             hidden = nxt
+        dispatch_deferred()
+        h0 = time.perf_counter()
         while lag:
             self._collect(lag.pop(0))
+        self._host("host_tail_collect_s", h0)
         if pending_outside is not None:
             names_o, og, sh = pending_outside
             self._report(names_o, self._finalize(names_o, outside, og, sh))

@@ -114,3 +114,40 @@ def test_rejects_bad_arguments(dgq):
     H = torch.zeros((12, 12), dtype=torch.float32, device="cuda")
     with pytest.raises(RuntimeError, match="align"):
         dgq.hessian_accum(x, H)
+
+
+def test_upper_only_accumulation_and_mirror(dgq):
+    """`dgq_hessian_accum_upper` over several batches followed by one `dgq_hessian_mirror` gives
+    the matrix `dgq_hessian_accum` builds, bit for bit (one token range per launch, so every
+    element receives the same additions in the same order)."""
+    g = torch.Generator(device="cuda").manual_seed(4)
+    for K in (264, 1024):
+        full = torch.zeros(K, K, device="cuda")
+        upper = torch.full((K, K), 7.0, device="cuda").tril(-1)      # junk below the diagonal
+        for _ in range(3):
+            x = torch.randn(2048, K, generator=g, device="cuda").bfloat16()
+            dgq.hessian_accum(x, full, 1.0, 1)
+            dgq.hessian_accum(x, upper, 1.0, 1, upper_only=True)
+        assert torch.equal(upper.tril(-1), torch.full((K, K), 7.0, device="cuda").tril(-1))
+        dgq.hessian_mirror(upper)
+        assert torch.equal(upper, full) and torch.equal(upper, upper.t())
+
+
+def test_long_accumulation_chains_stay_inside_the_bar(dgq):
+    """The tensor core's fp32 accumulator truncates, so the error of one launch grows with the
+    tokens it carries (one token range = one accumulation chain).  65536 tokens in one range is
+    what the model driver feeds per call; the result must stay well inside the 1e-3 bar, and
+    cutting the range (`splits`) must shrink the error in proportion."""
+    K, T = 1024, 65536
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(T, K, generator=g, device="cuda")
+    x[:, ::97] *= 20
+    xb = x.bfloat16()
+    want = xb.double().t() @ xb.double()
+    errs = {}
+    for splits in (1, 4):
+        H = torch.zeros(K, K, device="cuda")
+        dgq.hessian_accum(xb, H, 1.0, splits)
+        errs[splits] = float((H.double() - want).norm() / want.norm())
+    assert errs[1] <= 5e-4, errs
+    assert errs[4] <= 0.4 * errs[1], errs

@@ -1,16 +1,24 @@
 """End-to-end parity on the reference's own CPU-sized case: an OPT-125m-architecture model
 (random init, fp32, 12 decoder layers, d_model 768, FFN 3072, ReLU, vocab 50272), calibration
-ids uniform over the vocabulary from a seed, 4-bit, group 128, blocksize 128, percdamp 0.01,
-act-order off.  (Fewer and shorter sequences than the full case so that the CPU oracle
-finishes in about a minute; the shapes of every layer are the full ones.)
+128 sequences x 512 token ids uniform over the vocabulary from a seed, 4-bit, group 128,
+blocksize 128, percdamp 0.01, act-order off - configuration 1 at its stated size.
 
-The GPU driver quantizes all 72 linear layers.  Checked per layer, stage by stage: the
-Hessian the driver accumulated through its hooks against one the CPU accumulates from the
-unquantized model's activations (rounded to bf16, as the tensor-core path takes them; how
-far that rounding moves the Hessian is checked too) - within 1e-3; then the quantization
-against the oracle run on that same Hessian - reconstruction error within 2 % for every
-layer; codes >= 99.5 % identical with mismatches at adjacent levels only for every
-well-conditioned layer, and within the oracle's own sensitivity for the others (see below)."""
+The GPU driver quantizes all 72 decoder linears block by block.  Checked per layer, stage by
+stage:
+
+* the Hessian the driver accumulated through its hooks (bf16 inputs, tensor cores) against one
+  accumulated in fp64 from the unquantized model's activations rounded to bf16 (torch on the
+  device is the checker here; the bar is 1e-3, observed 5e-6);
+* the quantization against the oracle run on that same Hessian, in fp32 and - as the arbiter -
+  in fp64: reconstruction error within 2 % of the fp64 oracle's for every layer; codes >= 99.5 %
+  identical to the fp32 oracle's for every q/k/v/fc1 layer (48 of 72) and for the whole first
+  block.
+
+For the out_proj and fc2 layers of the deeper blocks the fp32 oracle is not a stable yardstick:
+at random init their inputs are strongly correlated, the Hessians nearly singular (eigenvalue
+spread ~1e5 against the damping), and the fp32 oracle itself differs from the fp64 oracle in
+0.2 - 1 % of the codes.  There the GPU (whose inverse factor is within 4x of LAPACK's fp32
+accuracy) must stay within twelve times the fp32 oracle's own distance from the fp64 arbiter."""
 import pytest
 import torch
 import torch.nn as nn
@@ -29,93 +37,77 @@ def test_opt125m_architecture_end_to_end(dgq):
                                  word_embed_proj_dim=768, activation_function="relu")
     torch.manual_seed(0)
     model = transformers.OPTForCausalLM(cfg).float().eval()
-    nseq, seqlen = 16, 320   # 5120 tokens: more than the widest input (3072), so every Hessian has full rank
+    nseq, seqlen = 128, 512
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 50272, (nseq, seqlen), generator=g)
     names = [n for n, m in model.named_modules()
              if isinstance(m, nn.Linear) and m.weight.numel() > 1000 and "lm_head" not in n]
     assert len(names) == 72
-
-    # CPU side: fp32 Hessians of the unquantized model, original weights
     mods = dict(model.named_modules())
-    H, H32 = {}, {}
     W0 = {n: mods[n].weight.data.clone() for n in names}
+
+    # checker: fp64 Hessians of the unquantized model, from inputs rounded to bf16 like the
+    # tensor-core path takes them, accumulated by torch on the device
+    model.cuda()
+    H64 = {}
 
     def hook(name):
         def f(mod, args):
-            x32 = args[0].detach().reshape(-1, args[0].shape[-1]).float()
-            H32[name] = H32.get(name, 0) + x32.t() @ x32
-            # the tensor-core path takes bf16 activations: the oracle gets the same inputs
-            x = x32.bfloat16().float()
-            H[name] = H.get(name, 0) + x.t() @ x
+            x = args[0].detach().reshape(-1, args[0].shape[-1]).bfloat16().double()
+            H64[name] = H64.get(name, 0) + x.t() @ x
         return f
     handles = [mods[n].register_forward_pre_hook(hook(n)) for n in names]
     with torch.no_grad():
-        for i in range(nseq):
-            model(input_ids=ids[i:i + 1], use_cache=False)
+        for i in range(0, nseq, 16):
+            model(input_ids=ids[i:i + 16].cuda(), use_cache=False)
     for h in handles:
         h.remove()
 
     # GPU side, through the public driver
     qz = DistributedGPTQuantizer(QuantizationConfig(bits=4, group_size=128, blocksize=128,
                                                     percdamp=0.01, actorder=False,
-                                                    calibration_samples=nseq), DistributedConfig())
-    calib = [{"input_ids": ids[i:i + 1], "use_cache": False} for i in range(nseq)]
+                                                    calibration_samples=nseq), DistributedConfig(),
+                                 calibration_batch_size=16)
     qz.keep_hessians = True
-    qz.quantize_model(model, calib, layers_to_quantize=names)
-    assert set(qz.quantized_layers) == set(names)
-    # q/k/v of a block share one Hessian
+    qz.quantize_model(model, ids, layers_to_quantize=names)
+    assert qz.mode_used == "block-wise" and set(qz.quantized_layers) == set(names)
     assert qz._leader["model.decoder.layers.3.self_attn.k_proj"] == \
         "model.decoder.layers.3.self_attn.q_proj" or \
         qz._leader["model.decoder.layers.3.self_attn.q_proj"] != "model.decoder.layers.3.self_attn.q_proj"
 
-    worst_match, worst_ratio, worst_h, worst_nonadj, strict = 1.0, 0.0, 0.0, 0.0, 0
-    loose = []
+    strict, worst = 0, {"h": 0.0, "match": 1.0, "recon": 0.0, "ratio": 0.0}
     for n in names:
-        # Rounding the fp32 activations to bf16 moves the Hessian by ~1e-3 * sqrt(K / tokens) in
-        # relative Frobenius norm: ~7e-4 at this test's 5120 tokens, ~2e-4 at the full case's
-        # 65536 tokens (the bar is 1e-3 there).
-        worst_h = max(worst_h, float((H[n] - H32[n]).norm() / H32[n].norm()))
-        assert worst_h <= 3e-3, n
-        # stage 1: the Hessian the driver accumulated (hooks, shared inputs) against the CPU's
         Hg = qz.hessians[n]
-        assert float((Hg - H[n]).norm() / H[n].norm()) <= 1e-3, n
-        # stage 2: quantization from that same Hessian
-        ref = O.gptq_quantize(W0[n], Hg, nseq, 4, 128, 128, 0.01, False)
+        herr = float((Hg.double() - H64[n].cpu()).norm() / H64[n].cpu().norm())
+        worst["h"] = max(worst["h"], herr)
+        assert herr <= 1e-3, (n, herr)
+        r32 = O.gptq_quantize(W0[n], Hg, nseq, 4, 128, 128, 0.01, False)
+        r64 = O.gptq_quantize(W0[n], Hg, nseq, 4, 128, 128, 0.01, False, dtype=torch.float64)
+        codes = O.unpack_f2(qz.packed[n][f"{n}.qweight"].cpu(), 4, W0[n].shape[1])
+        m32 = float((codes == r32["codes"]).float().mean())
+        m64 = float((codes == r64["codes"]).float().mean())
+        o64 = float((r32["codes"] == r64["codes"]).float().mean())
         Q = mods[n].weight.data.float().cpu()
-        r_gpu, r_ref = O.recon_error(W0[n], Q, H[n]), O.recon_error(W0[n], ref["Q"], H[n])
-        assert r_gpu <= 1.02 * r_ref, (n, r_gpu, r_ref)        # never worse than the oracle by > 2 %
-        recon_dev = abs(r_gpu - r_ref) / r_ref
-        codes = qz.packed[n][f"{n}.qweight"].cpu()
-        codes = O.unpack_f2(codes, 4, W0[n].shape[1])
-        diff = (codes.int() - ref["codes"].int()).abs()
-        match = float((diff == 0).float().mean())
-        nonadj = float((diff > 1).float().mean())
-        if match >= 0.995 and nonadj == 0.0 and recon_dev <= 0.02:
-            strict += 1
+        r_gpu = O.recon_error(W0[n], Q, Hg)
+        r_arb = O.recon_error(W0[n], r64["Q"].float(), Hg)
+        assert abs(r_gpu - r_arb) <= 0.02 * r_arb, (n, r_gpu, r_arb)
+        worst["recon"] = max(worst["recon"], abs(r_gpu / r_arb - 1))
+        worst["match"] = min(worst["match"], m32)
+        well_conditioned = not any(k in n for k in ("out_proj", "fc2")) or ".layers.0." in n
+        if well_conditioned:
+            assert m32 >= 0.995, (n, m32)
+            # mismatches are at adjacent levels, up to groups whose zero point moved by one
+            gi = r32["g_idx"].long()
+            z_gpu = qz.packed[n][f"{n}.zeros"].float().cpu()
+            lvl = (codes.float() - z_gpu[:, gi]) - (r32["codes"].float() - r32["zero"][:, gi])
+            assert float((lvl.abs() > 1).float().mean()) <= 5e-4, n
         else:
-            # At random init, a few blocks into the network, the activations are strongly
-            # correlated and the Hessians nearly singular (eigenvalue spread ~1e5 against the
-            # damping; worst for out_proj, which sees almost the same vector for every token, and
-            # for fc2): the codes are then unstable - the fp32 oracle itself changes 1-16 % of
-            # them, by up to 4 levels, when its Hessian is perturbed by 1e-5 relative, a
-            # hundredth of the Hessian tolerance.  Such layers must stay within what that
-            # perturbation does to the oracle (observed: q/k/v/fc1 >= 99.49 % identical).
-            gen = torch.Generator().manual_seed(len(n))
-            Hp = Hg * (1 + 1e-5 * torch.randn(Hg.shape, generator=gen))
-            Hp = (Hp + Hp.t()) / 2
-            rp = O.gptq_quantize(W0[n], Hp, nseq, 4, 128, 128, 0.01, False)
-            sens = 1.0 - float((rp["codes"] == ref["codes"]).float().mean())
-            assert 1.0 - match <= max(0.005, sens), (n, match, sens)
-            assert recon_dev <= 0.10, (n, r_gpu, r_ref)   # on these the oracle's own runs differ by percents
-            if not any(k in n for k in ("out_proj", "fc2")):
-                assert match >= 0.99, (n, match)      # q/k/v/fc1 stay close even so
-            loose.append((n, round(match, 4), round(sens, 4), int(diff.max())))
-        worst_nonadj = max(worst_nonadj, nonadj)
-        worst_match = min(worst_match, match)
-        worst_ratio = max(worst_ratio, abs(r_gpu / r_ref - 1))
-    print(f"{len(loose)} layers held to the sensitivity bar; worst five (name, match, oracle "
-          f"sensitivity, max level diff):", sorted(loose, key=lambda t: t[1])[:5])
-    assert strict >= 4, strict      # the first blocks, whose inputs are still well conditioned
-    print(f"72 layers, {strict} meet 99.5 % / adjacent-only outright: worst code match {worst_match:.4f}, worst recon deviation {worst_ratio:.4f}, "
-          f"worst bf16-rounding Hessian shift {worst_h:.2e}, worst non-adjacent fraction {worst_nonadj:.1e}")
+            ratio = (1 - m64) / max(1 - o64, 5e-4)
+            worst["ratio"] = max(worst["ratio"], ratio)
+            assert ratio <= 12.0, (n, m64, o64)
+            assert m32 >= 0.94, (n, m32)
+        strict += m32 >= 0.995
+    print(f"72 layers: {strict} with >= 99.5 % of the fp32 oracle's codes; worst Hessian error "
+          f"{worst['h']:.1e}, worst code match {worst['match']:.4f}, worst reconstruction-error "
+          f"deviation from the fp64 oracle {worst['recon']:.4f}, worst distance ratio {worst['ratio']:.1f}")
+    assert strict >= 49, strict     # measured: 50 (all q/k/v/fc1 and the first block)

@@ -128,3 +128,21 @@ def test_qlinear_many_rows(dgq, M, N_out, K, g, dtype):
     exact = (x.double() @ Wt.t())
     out_eps = {torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8}[dtype]
     assert float((got2.double().cpu() - exact).abs().max()) <= 1.01 * out_eps * float(exact.abs().max()) + 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_qlinear_many_rows_fractional_zero_points(dgq, dtype):
+    """Zero points that are not integers (the flat round-to-nearest helpers produce them) take the
+    kernel's fp32 dequantization instead of the two-instruction one."""
+    M, N_out, K, g = 96, 200, 768, 128
+    gen = torch.Generator().manual_seed(5)
+    codes = torch.randint(0, 16, (N_out, K), generator=gen).to(torch.uint8)
+    scales = (torch.rand(N_out, K // g, generator=gen) * 0.02 + 0.001).half()
+    zeros = (torch.rand(N_out, K // g, generator=gen) * 15).half()
+    zeros[::2] = zeros[::2].round()              # both kinds within one tile
+    x = torch.randn(M, K, generator=gen).to(dtype)
+    want = O.qlinear_forward(x, codes, scales, zeros, None, None, g)
+    got = dgq.qlinear_forward(x.cuda(), O.pack_f2(codes, 4).cuda(), scales.cuda(), zeros.cuda(), None,
+                              None, K, 4, g)
+    tol = {torch.float16: 8e-4, torch.bfloat16: 6e-3}[dtype]
+    assert float((got.float().cpu() - want).abs().max()) <= tol * float(want.abs().max())
