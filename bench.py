@@ -44,7 +44,13 @@ import sys
 import threading
 import time
 
-import torch
+# The model driver keeps a dozen and more streams busy (the main stream, four chain streams,
+# the inverse factor's side streams, the exchange streams).  With CUDA's default of 8 hardware
+# queues per device several of them share a queue, and a chain's short kernels then wait behind
+# a whole forward pass queued earlier on the main stream.  Must be set before CUDA starts.
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
+import torch  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)

@@ -35,7 +35,7 @@ namespace {
 constexpr int TILE_M = 128, TILE_N = 128, BK = 64;
 constexpr int A_BYTES = TILE_M * BK * 2, B_BYTES = TILE_N * BK * 2;     // 16 KB each
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 4;
+constexpr int STAGES = 6;
 constexpr int CONV_WARPS = 8;
 constexpr int THREADS = 32 * (2 + CONV_WARPS + 4);
 constexpr uint32_t TMEM_COLS = 256;
@@ -211,6 +211,9 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
                                : make_uint4(0u, 0u, 0u, 0u);
       };
       uint4 q0 = fetch(0), q1 = fetch(1), q2 = fetch(2), q3 = fetch(3);
+      // scale and zero of the next group are fetched a group ahead as well: a load that is
+      // needed at once would stall the warp for longer than a slice takes
+      __half s_next = srow[0], z_next = zrow[0];
       float sc = 0.f, zs = 0.f;
       uint32_t sub2 = 0u, mul2 = 0u;       // (BASE + zero, BASE + zero) and (scale, scale) as pairs of T
       bool short_path = false;
@@ -220,8 +223,9 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
         ++it;
         if (sl % slices_per_group == 0) {
           const int g = sl / slices_per_group;
-          sc = __half2float(srow[g]);
-          const float z = __half2float(zrow[g]);
+          sc = __half2float(s_next);
+          const float z = __half2float(z_next);
+          if (g + 1 < a.n_groups) { s_next = srow[g + 1]; z_next = zrow[g + 1]; }
           zs = z * sc;                                       // w = code * scale - zero * scale
           // integer zero points (every GPTQ zero is one) take the short path
           short_path = (z == rintf(z)) && fabsf(z) <= 64.f;
