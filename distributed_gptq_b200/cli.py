@@ -21,11 +21,16 @@ from __future__ import annotations
 import argparse
 import json
 import logging
+import os
 import sys
 import time
 from pathlib import Path
 
-import torch
+# The driver keeps many streams busy; with CUDA's default of 8 hardware queues per device the
+# chains' short kernels would queue behind whole forward passes.  Read when CUDA starts.
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
+import torch  # noqa: E402
 
 logger = logging.getLogger("distributed_gptq_b200.cli")
 
