@@ -206,7 +206,7 @@ def build_model(spec, n_layers: int, device, seed: int = 0):
 
 class ModelWorkload:
     def __init__(self, spec, variant, n_layers, rank, world, device, exchange, seed=0,
-                 true_sequential=False):
+                 true_sequential=False, blocks_in_flight=None):
         import torch.nn as nn
         from distributed_gptq_b200 import DistributedGPTQuantizer, QuantizationConfig
         from distributed_gptq_b200.coordinator import create_distributed_config
@@ -229,7 +229,8 @@ class ModelWorkload:
                                   calibration_samples=spec["nseq"], true_sequential=true_sequential)
         dcfg = create_distributed_config()
         dcfg.hessian_exchange = exchange
-        self.qz = DistributedGPTQuantizer(qcfg, dcfg, calibration_batch_size=spec["batch"])
+        self.qz = DistributedGPTQuantizer(qcfg, dcfg, calibration_batch_size=spec["batch"],
+                                          blocks_in_flight=blocks_in_flight)
         self.qz.profile = True
         self.host_out = None
         self.h2d_bytes = self.d2h_bytes = 0
@@ -646,6 +647,9 @@ def cpu_reference_outright(workload: str, variant: str):
 
 
 # ============================================================================= main
+E2E_BUDGET_S = 150.0      # time the host-input pass may take (see main)
+
+
 def main():
     # Libraries (NCCL's version banner, for one) may write to stdout; the JSON line must be
     # the only thing there, so everything else is sent to stderr.
@@ -669,6 +673,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="debugging: fewer decoder blocks than the named model (flagged in config)")
     ap.add_argument("--true-sequential", action="store_true")
+    ap.add_argument("--blocks-in-flight", type=int, default=None,
+                    help="blocks whose chains are enqueued but not collected (default: the "
+                         "library's choice, 2 up to two ranks, 4 above)")
     ap.add_argument("--sweep-chains", default="after", choices=["during", "after"],
                     help="sweep on several GPUs: enqueue a run's chain after all Hessians (default) or "
                          "right after its reduce, beside the remaining Hessian kernels (measured slower: "
@@ -735,7 +742,8 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        from distributed_gptq_b200.communication import group_options
+        dist.init_process_group("nccl", device_id=device, **group_options("nccl"))
     from distributed_gptq_b200 import _C
     _C.device_check()
 
@@ -768,7 +776,8 @@ def main():
     if is_model:
         n_layers = args.layers or spec["layers"]
         wl = ModelWorkload(spec, variant, n_layers, rank, world, device, args.exchange,
-                           true_sequential=args.true_sequential)
+                           true_sequential=args.true_sequential,
+                           blocks_in_flight=args.blocks_in_flight)
         step_dev, step_host = (lambda: wl.step(False)), (lambda: wl.step(True))
     else:
         wl = Sweep(rank, world, device, args.sweep_chains)
@@ -807,14 +816,18 @@ def main():
             wl.load_host_inputs()
             wl.X_dev = None
             torch.cuda.empty_cache()
-        for _ in range(min(2, max(1, args.warmup))):   # allocator / pinned-buffer warm-up
+        # The host-input pass repeats the same job: it takes as many steps as fit in about
+        # E2E_BUDGET_S (at least 3, at most --steps), so that a long --steps does not double
+        # the run; every rank derives the same count from the reduced step time.
+        e2e_steps = max(1, min(args.steps, max(3, int(E2E_BUDGET_S / max(ms_step / 1e3, 1e-3)))))
+        for _ in range(1 if ms_step > 2000 else min(2, max(1, args.warmup))):   # allocator / pinned buffers
             step_host()
-        ms_e2e = timed(step_host, max(1, args.steps), "host inputs")
+        ms_e2e = timed(step_host, e2e_steps, "host inputs")
         bt = torch.tensor([float(wl.h2d_bytes), float(wl.d2h_bytes)], device=device)
         if world > 1:
             dist.all_reduce(bt)
         e2e = {"value": ms_e2e / 1e3, "unit": unit, "h2d_bytes_per_step": int(bt[0]),
-               "d2h_bytes_per_step": int(bt[1])}
+               "d2h_bytes_per_step": int(bt[1]), "steps": e2e_steps}
 
     if rank == 0:
         pk = peaks()

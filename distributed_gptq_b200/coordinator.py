@@ -23,7 +23,7 @@ from typing import Dict, List, Sequence, Union
 import torch
 import torch.distributed as dist
 
-from .communication import CommunicationManager
+from .communication import CommunicationManager, group_options
 
 
 class QuantizationMode(Enum):
@@ -124,7 +124,8 @@ class DistributedGPTQCoordinator:
             dist.init_process_group(
                 backend=backend, init_method=f"tcp://{addr}:{self.config.master_port}",
                 rank=self.config.rank, world_size=self.config.world_size,
-                timeout=datetime.timedelta(seconds=self.config.init_timeout))
+                timeout=datetime.timedelta(seconds=self.config.init_timeout),
+                **group_options(backend))
             self._owns_group = True
         self.is_initialized = True
 

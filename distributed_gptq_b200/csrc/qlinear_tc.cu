@@ -5,16 +5,17 @@
 // 4-bit codes, two per byte with the even column in the low nibble (the QuantizedLinear
 // layout, models/layers.py:76-93), one fp16 scale/zero per output feature and group of
 // `group_size` consecutive columns (a multiple of 64).  The weights never exist in 16-bit
-// form in global memory: a CTA works on a 128-row x 128-feature tile of y and walks K in
-// slices of 64 columns; per slice
-//   - warp 0 fetches the 128 x 64 slice of x with one TMA box (128-byte swizzle): operand A;
+// form in global memory: a CTA works on a tile of y of 128 features x 128 rows (M <= 128) or
+// 256 rows (two sub-tiles that share the converted weights) and walks K in slices of 64
+// columns; per slice
+//   - warp 0 fetches the slice of x with one TMA box (128-byte swizzle): operand A;
 //   - warps 2-9 ("converters", two threads per output feature) read the feature's 32 bytes of
 //     packed codes straight from global memory (16 bytes per thread, four slices ahead: a load
 //     takes longer than a slice), turn them into 64 values (code - zero) * scale of the
 //     activation type and store them as the feature's 128-byte row of operand B, in the same
 //     swizzled layout a TMA box would have produced;
-//   - warp 1 issues four tcgen05.mma kind::f16 (M = 128 rows, N = 128 features, K = 16) into
-//     a 128-column fp32 accumulator in tensor memory;
+//   - warp 1 issues four tcgen05.mma kind::f16 (M = 128 rows, N = 128 features, K = 16) per
+//     sub-tile into that sub-tile's 128-column fp32 accumulator in tensor memory;
 // and warps 10-13 drain finished accumulators (two alternate), add the bias, round and store.
 // CTAs are persistent; tiles are ordered with the row tile running fastest, so the CTAs
 // running at one time share packed weights through L2.
@@ -32,17 +33,26 @@
 
 namespace {
 
-constexpr int TILE_M = 128, TILE_N = 128, BK = 64;
-constexpr int A_BYTES = TILE_M * BK * 2, B_BYTES = TILE_N * BK * 2;     // 16 KB each
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 6;
+constexpr int SUB_M = 128, TILE_N = 128, BK = 64;
+constexpr int SUB_A_BYTES = SUB_M * BK * 2, B_BYTES = TILE_N * BK * 2;  // 16 KB each
+constexpr int MAX_STAGES = 6;
 constexpr int CONV_WARPS = 8;
 constexpr int THREADS = 32 * (2 + CONV_WARPS + 4);
-constexpr uint32_t TMEM_COLS = 256;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+
+// A tile of y is MT sub-tiles of 128 rows against the same 128 features: the converted slice
+// of weights (the expensive operand) then serves MT products.  192 KB of stages either way.
+template <int MT> struct Shape {
+  static constexpr int TILE_M = SUB_M * MT;
+  static constexpr int A_BYTES = SUB_A_BYTES * MT;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = MT == 1 ? 6 : 4;
+  static constexpr uint32_t ACC_COLS = TILE_N * MT;          // one accumulator set
+  static constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // two sets alternate
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+};
 
 struct Control {
-  uint64_t full[STAGES], conv[STAGES], empty[STAGES];
+  uint64_t full[MAX_STAGES], conv[MAX_STAGES], empty[MAX_STAGES];
   uint64_t tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   int abort;
@@ -98,9 +108,13 @@ __device__ __forceinline__ float bias_at(const void* b, int dt, int n) {
   return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[n]);
 }
 
-template <typename T>
+template <typename T, int MT>
 __global__ void __launch_bounds__(THREADS, 1)
 qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
+  using S = Shape<MT>;
+  constexpr int TILE_M = S::TILE_M, A_BYTES = S::A_BYTES, STAGE_BYTES = S::STAGE_BYTES;
+  constexpr int STAGES = S::STAGES;
+  constexpr uint32_t TMEM_COLS = S::TMEM_COLS, ACC_COLS = S::ACC_COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* stages = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -157,7 +171,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = tc05::make_instr_desc(Cvt<T>::FMT, false, false, TILE_M, TILE_N);
+      constexpr uint32_t idesc = tc05::make_instr_desc(Cvt<T>::FMT, false, false, SUB_M, TILE_N);
       uint32_t it = 0, lt = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++lt) {
@@ -167,7 +181,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
           break;
         }
         tc05::fence_after_sync();
-        const uint32_t acc = tmem_base + ab * TILE_N;
+        const uint32_t acc = tmem_base + ab * ACC_COLS;
         for (int s_ = 0; s_ < p.n_slices; ++s_, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!tc05::mbar_wait_bounded(&ctl->full[s], ph, abort_flag) ||
@@ -182,9 +196,13 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // both operands are K-major rows of 128 bytes: 16 elements = 32 bytes further along
-            const uint64_t da = tc05::make_smem_desc(a_base + k * 32, 0, 1024);
             const uint64_t db = tc05::make_smem_desc(b_base + k * 32, 0, 1024);
-            tc05::umma_bf16(acc, da, db, idesc, (s_ | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              // sub-tile mt: rows 128 mt .. of the box, 16 KB further; its own 128 columns
+              const uint64_t da = tc05::make_smem_desc(a_base + mt * SUB_A_BYTES + k * 32, 0, 1024);
+              tc05::umma_bf16(acc + mt * TILE_N, da, db, idesc, (s_ | k) != 0 ? 1u : 0u);
+            }
           }
           tc05::umma_commit(&ctl->empty[s]);
         }
@@ -292,11 +310,13 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
         break;
       }
       tc05::fence_after_sync();
-      const int row = tm * TILE_M + q * 32 + lane;           // this thread's row of y
 #pragma unroll 1
-      for (int chunk = 0; chunk < TILE_N / 32; ++chunk) {
+      for (int cc = 0; cc < MT * (TILE_N / 32); ++cc) {
+        const int mt = cc / (TILE_N / 32), chunk = cc % (TILE_N / 32);
+        const int row = tm * TILE_M + mt * SUB_M + q * 32 + lane;   // this thread's row of y
         uint32_t v[32];
-        tc05::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * TILE_N + chunk * 32, v);
+        tc05::tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * ACC_COLS + mt * TILE_N +
+                                chunk * 32, v);
         tc05::tmem_ld_wait();
         const int n0 = tn * TILE_N + chunk * 32;
         if (row < a.M && n0 < a.N_out) {
@@ -357,33 +377,51 @@ bool qlinear_tc_supported(const QLinearTcArgs& a) {
   return true;
 }
 
-bool qlinear_tc_launch(const QLinearTcArgs& a, cudaStream_t st) {
-  static DgqDeviceOnce once;
-  if (!once.run([] {
-        const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
-        return cudaFuncSetAttribute(qlinear_tc_kernel<__half>, at, (int)SMEM_BYTES) == cudaSuccess &&
-               cudaFuncSetAttribute(qlinear_tc_kernel<__nv_bfloat16>, at, (int)SMEM_BYTES) == cudaSuccess;
-      }))
-    return false;
+namespace {
+
+template <int MT>
+bool launch_shape(const QLinearTcArgs& a, cudaStream_t st) {
+  using S = Shape<MT>;
   CUtensorMap map_x;
   const CUtensorMapDataType dt = a.dtype == DGQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (!tc05::make_tensor_map_2d(&map_x, dt, 2, a.x, (uint64_t)a.M, (uint64_t)a.K,
-                                (uint64_t)a.K * 2, TILE_M, BK))
+                                (uint64_t)a.K * 2, S::TILE_M, BK))
     return false;
   Params p;
   p.a = a;
-  p.tiles_m = (int)dgq_cdiv(a.M, TILE_M);
+  p.tiles_m = (int)dgq_cdiv(a.M, S::TILE_M);
   p.tiles_n = (int)dgq_cdiv(a.N_out, TILE_N);
   p.n_tiles = p.tiles_m * p.tiles_n;
   p.n_slices = a.K / BK;
   const unsigned grid = (unsigned)std::min(p.n_tiles, dgq_sm_count());
   if (a.dtype == DGQ_F16)
-    qlinear_tc_kernel<__half><<<grid, THREADS, SMEM_BYTES, st>>>(map_x, p);
+    qlinear_tc_kernel<__half, MT><<<grid, THREADS, S::SMEM_BYTES, st>>>(map_x, p);
   else
-    qlinear_tc_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, st>>>(map_x, p);
+    qlinear_tc_kernel<__nv_bfloat16, MT><<<grid, THREADS, S::SMEM_BYTES, st>>>(map_x, p);
   dgq_note_launches(1);
   return cudaGetLastError() == cudaSuccess;
+}
+
+template <typename K>
+bool set_smem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) ==
+         cudaSuccess;
+}
+
+}  // namespace
+
+bool qlinear_tc_launch(const QLinearTcArgs& a, cudaStream_t st) {
+  static DgqDeviceOnce once;
+  if (!once.run([] {
+        return set_smem(qlinear_tc_kernel<__half, 1>, Shape<1>::SMEM_BYTES) &&
+               set_smem(qlinear_tc_kernel<__nv_bfloat16, 1>, Shape<1>::SMEM_BYTES) &&
+               set_smem(qlinear_tc_kernel<__half, 2>, Shape<2>::SMEM_BYTES) &&
+               set_smem(qlinear_tc_kernel<__nv_bfloat16, 2>, Shape<2>::SMEM_BYTES);
+      }))
+    return false;
+  // above one sub-tile of rows the 256-row tile halves the conversions per product
+  return a.M > SUB_M ? launch_shape<2>(a, st) : launch_shape<1>(a, st);
 }
 
 }  // namespace dgq

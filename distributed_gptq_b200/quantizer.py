@@ -165,7 +165,7 @@ class DistributedGPTQuantizer:
     def __init__(self, quantization_config: Optional[QuantizationConfig] = None,
                  distributed_config: Optional[DistributedConfig] = None,
                  calibration_batch_size: int = 8, blockwise: Union[str, bool] = "auto",
-                 share_weights: bool = True):
+                 share_weights: bool = True, blocks_in_flight: Optional[int] = None):
         self.quant_config = quantization_config or QuantizationConfig()
         self.quant_config.validate()
         self.dist_config = distributed_config or create_distributed_config()
@@ -179,6 +179,14 @@ class DistributedGPTQuantizer:
         # rank ends with the same model (the reference's behaviour, coordinator.py:231-233);
         # False leaves the weights of layers another rank quantized untouched on this rank
         self.share_weights = share_weights
+        # block-wise, one-shot: how many blocks may have their chains enqueued but their results
+        # not collected.  The host stands still in a collect, and the main stream runs dry if
+        # that lasts longer than the passes queued ahead; with many ranks a block's pass is
+        # short against its exchange + chain + broadcast, so more blocks are kept in flight
+        # (each holds its Hessians on their owners: 0.7 GB for a Llama-7B block).
+        if blocks_in_flight is None:
+            blocks_in_flight = 2 if self.dist_config.world_size <= 2 else 4
+        self.blocks_in_flight = max(1, int(blocks_in_flight))
         self.quantized_layers: Dict[str, dict] = {}
         self.quantization_errors: Dict[str, float] = {}
         self.packed: Dict[str, Dict[str, torch.Tensor]] = {}
@@ -376,7 +384,7 @@ class DistributedGPTQuantizer:
             # there since (the next block's pass).
             main = torch.cuda.current_stream(co.device)
             if self._xchg_stream is None:
-                self._xchg_stream = torch.cuda.Stream(device=co.device)
+                self._xchg_stream = torch.cuda.Stream(device=co.device, priority=-1)
             xs = self._xchg_stream
             if after is not None:
                 xs.wait_event(after)
@@ -471,7 +479,7 @@ class DistributedGPTQuantizer:
         co, dc = self.coordinator, self.dist_config
         dev = co.device
         if self._share_stream is None:
-            self._share_stream = torch.cuda.Stream(device=dev)
+            self._share_stream = torch.cuda.Stream(device=dev, priority=-1)
         shared = []
         main = torch.cuda.current_stream(dev)
         for owner in sorted({g.owner for g in groups}):
@@ -878,7 +886,7 @@ class DistributedGPTQuantizer:
                 nxt = [self._block_call(block, h, captured[i][0], captured[i][1])
                        for i, h in enumerate(hidden)]
                 self._span("forward_s", t0)
-            elif len(lag) > 2:
+            elif len(lag) > self.blocks_in_flight:
                 self._collect(lag.pop(0))    # bounds how far the host runs ahead of the device
             hidden = nxt
         dispatch_deferred()

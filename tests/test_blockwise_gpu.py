@@ -76,6 +76,20 @@ def test_blockwise_equals_whole_model(dgq):
         assert torch.equal(pa, pb), na
 
 
+@pytest.mark.parametrize("depth", [1, 4])
+def test_blocks_in_flight_do_not_change_results(dgq, depth):
+    """How many blocks have chains enqueued but not collected is scheduling only."""
+    qa, ma = _run()
+    qb, mb = _run(blocks_in_flight=depth)
+    assert qa.blocks_in_flight == 2 and qb.blocks_in_flight == depth
+    for n in qa.packed:
+        for k in qa.packed[n]:
+            assert torch.equal(qa.packed[n][k], qb.packed[n][k]), (n, k)
+        assert qa.quantization_errors[n] == qb.quantization_errors[n]
+    for (na, pa), (nb, pb) in zip(ma.state_dict().items(), mb.state_dict().items()):
+        assert torch.equal(pa, pb), na
+
+
 def test_stacked_group_equals_single_layers(dgq):
     """q/k/v quantized as one stacked matrix == each quantized by itself with the same Hessian."""
     from distributed_gptq_b200 import GPTQ
