@@ -647,6 +647,8 @@ def cpu_reference_outright(workload: str, variant: str):
 
 
 # ============================================================================= main
+EXCHANGE_NAMES = {"owner": "reduce to owner", "all_reduce": "all_reduce",
+                  "peer": "summed by the Hessian kernels in the owner's buffer (peer reductions)"}
 E2E_BUDGET_S = 150.0      # time the host-input pass may take (see main)
 
 
@@ -669,7 +671,10 @@ def main():
     ap.add_argument("--workload", default="llama7b", choices=["llama7b", "sweep", "opt1.3b",
                                                               "llama13b", "opt125m"])
     ap.add_argument("--variant", default=None, help="quantization setting of a model workload")
-    ap.add_argument("--exchange", default="owner", choices=["owner", "all_reduce"])
+    ap.add_argument("--exchange", default="owner", choices=["owner", "all_reduce", "peer"],
+                    help="how partial Hessians are summed: NCCL reduce to the owner, NCCL "
+                         "all_reduce (the reference's flow), or by the Hessian kernels "
+                         "themselves into the owner's buffer over NVLink")
     ap.add_argument("--layers", type=int, default=0,
                     help="debugging: fewer decoder blocks than the named model (flagged in config)")
     ap.add_argument("--true-sequential", action="store_true")
@@ -701,7 +706,7 @@ def main():
         if variant not in spec["variants"]:
             raise SystemExit(f"--variant must be one of {list(spec['variants'])}")
     par = (f"dp{world} calibration + layer-parallel quantization, Hessian exchange: "
-           f"{'reduce to owner' if args.exchange == 'owner' else 'all_reduce'}") if world > 1 \
+           f"{EXCHANGE_NAMES[args.exchange]}") if world > 1 \
         else "single GPU"
 
     if args.impl == "reference":

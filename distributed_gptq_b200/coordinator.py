@@ -45,7 +45,9 @@ class DistributedConfig:
     init_timeout: int = 1800
     # extension: "owner" reduces each Hessian to the rank that quantizes the layer and
     # spreads the layers over the ranks; "all_reduce" reproduces the reference's flow
-    # (every rank receives every Hessian and quantizes every layer).
+    # (every rank receives every Hessian and quantizes every layer); "peer" is "owner" with
+    # the sum over ranks done by the Hessian kernels themselves, which accumulate straight
+    # into the owner's buffer over NVLink (block-wise driver; see peer.py).
     hessian_exchange: str = "owner"
 
     @property

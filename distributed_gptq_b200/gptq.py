@@ -95,6 +95,9 @@ class GPTQ:
         # reduction traffic of every batch); the lower part is filled in when the matrix is
         # read: by the `H` property and before quantization
         self._lower_stale = False
+        # set by a driver that lends this object a Hessian buffer other ranks' kernels
+        # accumulate into as well: the buffer is zeroed as soon as quantization has read it
+        self._recycle = False
 
     # ------------------------------------------------------------------ helpers
     def _weight_matrix(self) -> torch.Tensor:
@@ -309,6 +312,8 @@ def quantize_group_launch(members: List["GPTQ"]) -> Dict[str, torch.Tensor]:
     if lead.actorder:
         perm, invperm = _C.actorder_perm(H, scale)
     Hp, dead = _C.hessian_prepare(H, scale, lead.percdamp, perm)
+    if lead._recycle:           # a lent buffer: hand it back empty
+        lead._Hbuf.zero_()
     Wp = _C.permute_cols(W, perm, dead)
     del W
     info = _C.new_info(dev)

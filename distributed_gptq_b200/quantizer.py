@@ -36,7 +36,7 @@ from typing import Callable, Dict, Iterable, List, Optional, Tuple, Union
 import torch
 import torch.nn as nn
 
-from . import _C, io
+from . import _C, io, peer
 from .coordinator import (DistributedConfig, DistributedGPTQCoordinator, assign_owners,
                           create_distributed_config, layer_cost)
 from .gptq import GPTQ, quantize_group_launch
@@ -157,6 +157,7 @@ class _Group:
         self.mine = True
         self.future = None          # chain enqueued -> (device status tensors, packed dicts)
         self.reduce_work = None
+        self.peer = False           # Hessian accumulated in the owner's buffer by every rank
 
 
 class DistributedGPTQuantizer:
@@ -203,6 +204,13 @@ class DistributedGPTQuantizer:
         self.hessians: Dict[str, torch.Tensor] = {}
         self._leader: Dict[str, str] = {}
         self.mode_used: Optional[str] = None
+        # hessian_exchange == "peer": symmetric buffers, the grouping of a block learned from
+        # the first one, and how many blocks have been given a generation of buffers
+        self._arena: Optional[peer.PeerArena] = None
+        self._arena_failed = False
+        self._group_pattern: Optional[Dict[str, str]] = None
+        self._peer_counter = 0
+        self.peer_groups = 0        # groups of the last run whose Hessians were summed by the kernels
 
     # ------------------------------------------------------------------ discovery
     def _find_layers_to_quantize(self, model: nn.Module) -> Dict[str, nn.Module]:
@@ -363,11 +371,13 @@ class DistributedGPTQuantizer:
         everything queued on the main stream so far is waited for."""
         cfg, co, dc = self.quant_config, self.coordinator, self.dist_config
         world, rank = dc.world_size, dc.rank
-        owner_mode = dc.hessian_exchange == "owner" and world > 1
+        owner_mode = dc.hessian_exchange in ("owner", "peer") and world > 1
         costs = [sum(layer_cost(*q._weight_matrix().shape) for q in g.q) for g in groups]
         order = sorted(range(len(groups)), key=lambda i: (-costs[i], i))
         for i in order:
             g = groups[i]
+            if g.peer:              # owner chosen before the pass (_peer_prepare)
+                continue
             if owner_mode:
                 g.owner = min(range(world), key=lambda k: (load[k], k))
                 load[g.owner] += costs[i]
@@ -390,7 +400,27 @@ class DistributedGPTQuantizer:
                 xs.wait_event(after)
             else:
                 xs.wait_stream(main)
+            summed = [g for g in groups if g.peer]
+            if summed:
+                # Their Hessians are complete on the owners once every rank's pass is: what is
+                # left of the exchange is a barrier.  It carries the status words of the ranks'
+                # Hessian kernels (maximum over ranks), which the owner reports with its own.
+                with torch.cuda.stream(xs):
+                    for g in summed:
+                        g.q[0]._info.record_stream(xs)
+                    words = torch.stack([g.q[0]._info for g in summed])
+                    t0 = self._mark()
+                    work = co.comm.all_reduce_tensor(words, op=torch.distributed.ReduceOp.MAX,
+                                                     async_op=True)
+                    self._span("exchange_s", t0, work)
+                for i, g in enumerate(summed):
+                    g.reduce_work = work
+                    if g.mine:
+                        g.q[0]._info = words[i]
+                self.peer_groups += len(summed)
             for g in groups:    # same order on every rank
+                if g.peer:
+                    continue
                 lead = g.q[0]
                 if lead._Hbuf is None:   # this rank saw no sample: it still takes part
                     K8 = (lead.columns + 7) // 8 * 8
@@ -431,6 +461,82 @@ class DistributedGPTQuantizer:
                 return status, packed
 
             g.future = self._pool.submit(chain, after=after)
+
+    # ------------------------------------------------------------------ Hessians summed by the kernels
+    def _peer_begin(self) -> bool:
+        """Start of a block-wise run with ``hessian_exchange == "peer"``: an arena a failed run
+        left half-used is cleared on every rank."""
+        co, dc = self.coordinator, self.dist_config
+        self._group_pattern, self._peer_counter, self.peer_groups = None, 0, 0
+        if dc.hessian_exchange != "peer" or dc.world_size <= 1 or co.device.type != "cuda":
+            return False
+        if self._arena is not None and self._arena.group is not torch.distributed.group.WORLD:
+            self._arena = None              # its process group is gone
+        if self._arena is not None:
+            flag = torch.tensor([int(self._arena.dirty)], dtype=torch.int32, device=co.device)
+            co.comm.all_reduce_tensor(flag, op=torch.distributed.ReduceOp.MAX)
+            if int(flag.item()):
+                self._arena.clear()
+                torch.cuda.synchronize(co.device)
+                co.comm.barrier()
+                self._arena.dirty = False
+        return True
+
+    def _peer_prepare(self, head: str, names_b: List[str], quantizers: Dict[str, GPTQ],
+                      load: List[float]) -> Optional[Dict[str, int]]:
+        """Before a block's pass: predicts the block's groups from the first block's, chooses
+        their owners and points every predicted leader's Hessian at its owner's buffer, so that
+        ``add_batch`` on every rank accumulates there.  Returns ``{leader: owner}`` or ``None``
+        (no prediction, or no symmetric memory: the block takes the NCCL reduction).  Every
+        rank computes the same plan from the same names, shapes and loads."""
+        co, dc = self.coordinator, self.dist_config
+        pat = self._group_pattern
+        if pat is None or self._arena_failed:
+            return None
+        rel = {n: n[len(head):] for n in names_b}
+        if any(not n.startswith(head) or rel[n] not in pat for n in names_b):
+            return None
+        leaders = [n for n in names_b if pat[rel[n]] == rel[n]]
+        members = {l: [n for n in names_b if head + pat[rel[n]] == l] for l in leaders}
+        widths = [(quantizers[l].columns + 7) // 8 * 8 for l in leaders]
+        offsets, gen_bytes = peer.generation_layout(widths)
+        generations = self.blocks_in_flight + 2     # see the collect rule in _quantize_blockwise
+        if self._arena is not None and not self._arena.fits(gen_bytes, generations):
+            self._arena = None
+        if self._arena is None:
+            self._arena = peer.make_arena(co.device, gen_bytes, generations, co.comm.barrier)
+            if self._arena is None:
+                self._arena_failed = True
+                return None
+        arena = self._arena
+        gen = self._peer_counter % arena.generations
+        self._peer_counter += 1
+        costs = [sum(layer_cost(*quantizers[m]._weight_matrix().shape) for m in members[l])
+                 for l in leaders]
+        plan: Dict[str, int] = {}
+        for i in sorted(range(len(leaders)), key=lambda i: (-costs[i], i)):
+            owner = min(range(dc.world_size), key=lambda k: (load[k], k))
+            load[owner] += costs[i]
+            q = quantizers[leaders[i]]
+            q._Hbuf = arena.view(owner, gen, offsets[i], widths[i])
+            q._info = _C.new_info(co.device)
+            q._lower_stale = True
+            q._recycle = owner == dc.rank       # the owner zeroes it once its chain has read it
+            plan[leaders[i]] = owner
+        arena.dirty = True
+        return plan
+
+    def _mark_peer(self, groups: List[_Group], plan: Optional[Dict[str, int]]) -> None:
+        """After the pass: a group whose leader was given an owner's buffer is complete there,
+        whatever its members turned out to be; a leader the prediction missed has accumulated
+        into a buffer of its own and takes the NCCL reduction."""
+        if not plan:
+            return
+        for g in groups:
+            if g.leader in plan:
+                g.peer = True
+                g.owner = plan[g.leader]
+                g.mine = g.owner == self.dist_config.rank
 
     def _share_layout(self, groups: List[_Group], owner: int):
         """Pieces of the flat buffer rank ``owner`` sends for one block: for every layer it
@@ -692,6 +798,7 @@ class DistributedGPTQuantizer:
             samples = co.shard_calibration(samples)
             batches = make_batches(samples, self.calibration_batch_size)
             self.timings = {}
+            self.peer_groups = 0
             self._spans = []
             self._probe_next = 0
             self._probe_streams = ([torch.cuda.Stream(device=co.device) for _ in range(8)]
@@ -813,6 +920,13 @@ class DistributedGPTQuantizer:
         else:
             pending_outside = None
 
+        # Hessians summed by the kernels themselves: block b accumulates in generation
+        # b mod (blocks_in_flight + 2) of the owners' buffers.  The passes of block b are
+        # enqueued after the collects of iteration b - 1, which leave at most blocks_in_flight
+        # blocks (the youngest being b - 2) uncollected: the block that used the generation
+        # before, b - blocks_in_flight - 2, has been collected by every rank, so its owners'
+        # chains have read and zeroed the buffers.
+        peer_mode = self._peer_begin()
         lag: List[tuple] = []       # blocks whose chains are enqueued but not collected yet
         # One-shot mode: the chains of block b are enqueued only after the pass of block b+1.
         # A chain is a thousand and more launches on a stream that cannot start before its
@@ -821,18 +935,36 @@ class DistributedGPTQuantizer:
         # the next pass already queued, the main stream has work for that time.
         deferred: Optional[tuple] = None
 
+        unshared: List[list] = []   # dispatched, results not yet on their way to the other ranks
+
+        def share_pending():
+            while unshared:
+                it = unshared.pop(0)
+                it[4] = self._share_block(it[3])
+
         def dispatch_deferred():
             nonlocal deferred
             if deferred is None:
                 return
-            b_, names_, targets_, quantizers_, shard_, ev_ = deferred
+            b_, names_, targets_, quantizers_, shard_, ev_, plan_ = deferred
             deferred = None
             h0_ = time.perf_counter()
             groups_ = self._groups_of(names_, quantizers_)
+            self._mark_peer(groups_, plan_)
             self._dispatch(groups_, load, after=ev_)
-            shared_ = self._share_block(groups_) if share else None
+            # The broadcasts of a block are issued after the exchange of the next one: the
+            # collectives of a process group run in the order of issue, and a broadcast waits
+            # for its owner's chain; issued at once it would hold back the next block's
+            # Hessian exchange - and with it that block's chains - until this block's chains
+            # are done, one block after the other.
+            share_pending()
+            item = [b_, names_, targets_, groups_, None, shard_]
+            if share:
+                unshared.append(item)
+                if sequential:
+                    share_pending()
             self._host("host_enqueue_chains_s", h0_)
-            lag.append((b_, names_, targets_, groups_, shared_, shard_))
+            lag.append(item)
 
         for b, block in enumerate(blocks):
             targets = per_block[b]
@@ -844,6 +976,9 @@ class DistributedGPTQuantizer:
                 if sequential:      # later blocks are calibrated on the quantized model
                     io.apply_block_weights(targets, resumed)
             quantizers = self._new_quantizers(targets) if resumed is None else {}
+            head = f"{prefix}{b}."
+            plan_b = (self._peer_prepare(head, names_b, quantizers, load)
+                      if peer_mode and resumed is None and targets else None)
             bstate = {"first": True, "accumulate": not discovery_only}
             handles = self._hook_layers(targets, quantizers, bstate) if resumed is None else []
             nxt = []
@@ -876,7 +1011,11 @@ class DistributedGPTQuantizer:
                 self._leader.update({n: bstate["leader"].get(n, n) for n in names_b})
                 if b == 0:
                     self._check_grouping(names_b)
-                deferred = (b, names_b, targets, quantizers, shard, done_b)
+                if peer_mode and self._group_pattern is None:
+                    # what the later blocks' groups are predicted from
+                    self._group_pattern = {n[len(head):]: self._leader[n][len(head):]
+                                           for n in names_b if n.startswith(head)}
+                deferred = (b, names_b, targets, quantizers, shard, done_b, plan_b)
                 if sequential:
                     dispatch_deferred()
             if sequential and targets:
@@ -887,9 +1026,12 @@ class DistributedGPTQuantizer:
                        for i, h in enumerate(hidden)]
                 self._span("forward_s", t0)
             elif len(lag) > self.blocks_in_flight:
+                if lag[0][4] is None:       # cannot be collected before its results travel
+                    share_pending()
                 self._collect(lag.pop(0))    # bounds how far the host runs ahead of the device
             hidden = nxt
         dispatch_deferred()
+        share_pending()
         h0 = time.perf_counter()
         while lag:
             self._collect(lag.pop(0))
@@ -908,6 +1050,8 @@ class DistributedGPTQuantizer:
             self._report(names_o, self._finalize(names_o, outside, og, sh))
         if self._pool is not None:
             self._pool.join()
+        if self._arena is not None:
+            self._arena.dirty = False       # every buffer has been read and zeroed again
         return True
 
     def _collect(self, item) -> None:

@@ -52,7 +52,8 @@ def _run(rank, world, port, mode, out_path, kind="mlp"):
     assert kind == "mlp" or qz.mode_used.startswith("block-wise")
     state = {k: v.detach().cpu() for k, v in model.state_dict().items()}
     packed = {n: {k: v.cpu() for k, v in e.items()} for n, e in qz.packed.items()}
-    torch.save({"state": state, "packed": packed, "errors": qz.quantization_errors},
+    torch.save({"state": state, "packed": packed, "errors": qz.quantization_errors,
+                "peer_groups": qz.peer_groups, "arena_failed": qz._arena_failed},
                f"{out_path}.{rank}")
 
 
@@ -101,12 +102,15 @@ def test_two_ranks_match_one(dgq, tmp_path, mode):
 
 
 @pytest.mark.parametrize("kind,mode", [("decoder", "owner"), ("decoder", "all_reduce"),
-                                       ("decoder-sequential", "owner")])
+                                       ("decoder-sequential", "owner"), ("decoder", "peer"),
+                                       ("decoder-sequential", "peer")])
 def test_two_ranks_block_by_block(dgq, tmp_path, kind, mode):
     """The block-by-block driver on two ranks: per-block reduce to the owner, chains on the
     owners, one flat broadcast per owner and block; true-sequential re-runs every block with
     the weights it received.  Both ranks must end with the same model, equal to the
-    single-GPU result up to the summation order of the partial Hessians."""
+    single-GPU result up to the summation order of the partial Hessians.  ``peer``: from the
+    second block on both ranks' Hessian kernels accumulate straight into the owner's buffer
+    (symmetric memory) and a barrier stands where the reduction was."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from distributed_gptq_b200 import DistributedGPTQuantizer
@@ -126,6 +130,8 @@ def test_two_ranks_block_by_block(dgq, tmp_path, kind, mode):
         assert p.exitcode == 0
     res = [torch.load(f"{out}.{r}") for r in range(2)]
     assert len(res[0]["packed"]) == 16 and set(res[0]["errors"]) == set(single.quantization_errors)
+    for r in res:       # blocks 1 and 2: (q, k, v), up, down each; block 0 teaches the grouping
+        assert r["peer_groups"] == (6 if mode == "peer" and not r["arena_failed"] else 0)
     for k in res[0]["state"]:
         assert torch.equal(res[0]["state"][k], res[1]["state"][k]), k
     for n in res[0]["packed"]:
