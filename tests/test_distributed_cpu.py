@@ -223,6 +223,72 @@ def test_share_layout_is_aligned_and_deterministic():
         assert qz._share_layout([g1, g2], 1) == (pieces, total)
 
 
+def test_peer_plan_is_the_same_on_every_rank(monkeypatch):
+    """``hessian_exchange == "peer"``: before a block's pass every rank predicts the block's
+    groups from the first block's, chooses the same owners and takes the same slot of the
+    same generation of the arena; only the owner hands the buffer back zeroed."""
+    import torch.nn as nn
+    from distributed_gptq_b200 import DistributedGPTQuantizer, QuantizationConfig, _C, peer
+    from distributed_gptq_b200.coordinator import DistributedConfig
+    from distributed_gptq_b200.quantizer import _Group
+
+    offsets, size = peer.generation_layout([4096, 4096, 11008])
+    assert offsets == [0, 4096 * 4096 * 4, 2 * 4096 * 4096 * 4] and size % peer.ALIGN == 0
+    assert peer.generation_layout([100])[1] == 40192                 # 40000 padded to 256 bytes
+
+    class FakeQ:
+        def __init__(self, layer):
+            self.layer, self.columns = layer, layer.weight.shape[1]
+            self._Hbuf = self._info = None
+            self._recycle = False
+
+        def _weight_matrix(self):
+            return self.layer.weight.data
+
+    class FakeArena:
+        generations, dirty = 4, False
+
+        def fits(self, b, g):
+            return True
+
+        def view(self, rank, gen, off, K8):
+            return ("slot", rank, gen, off, K8)
+
+    monkeypatch.setattr(_C, "new_info", lambda dev: torch.zeros(2, dtype=torch.int32))
+    pattern = {"q": "q", "k": "q", "v": "q", "up": "up", "down": "down"}
+    shapes = {"q": (64, 64), "k": (64, 64), "v": (64, 64), "up": (160, 64), "down": (64, 160)}
+    plans = []
+    for rank in range(2):
+        qz = DistributedGPTQuantizer(QuantizationConfig(),
+                                     DistributedConfig(world_size=2, rank=rank, hessian_exchange="peer"))
+        assert qz.blocks_in_flight == 2
+        qz._arena, qz._group_pattern = FakeArena(), dict(pattern)
+        load, seen = [0.0, 0.0], []
+        for b in (1, 2, 3, 4, 5):
+            head = f"layers.{b}."
+            qs = {head + n: FakeQ(nn.Linear(i, o, bias=False)) for n, (o, i) in shapes.items()}
+            plan = qz._peer_prepare(head, list(qs), qs, load)
+            assert set(plan) == {head + "q", head + "up", head + "down"}
+            for lead, owner in plan.items():
+                slot = qs[lead]._Hbuf
+                assert slot[1] == owner and slot[2] == (b - 1) % 4 and qs[lead]._recycle == (owner == rank)
+                assert qs[lead]._info is not None
+            assert qs[head + "k"]._Hbuf is None
+            groups = [_Group(head + "q", [head + "q", head + "k", head + "v"], qs),
+                      _Group(head + "up", [head + "up"], qs), _Group(head + "down", [head + "down"], qs),
+                      _Group(head + "k", [head + "k"], qs)]      # a leader the prediction missed
+            qz._mark_peer(groups, plan)
+            assert [g.peer for g in groups] == [True, True, True, False]
+            assert all(g.mine == (g.owner == rank) for g in groups[:3])
+            seen.append({k: (v, qs[k]._Hbuf) for k, v in plan.items()})
+        assert abs(load[0] - load[1]) <= max(load) * 0.5
+        plans.append((seen, load))
+        # a block whose names the pattern does not know takes the NCCL reduction
+        odd = {"layers.9.other": FakeQ(nn.Linear(8, 8))}
+        assert qz._peer_prepare("layers.9.", list(odd), odd, load) is None
+    assert plans[0] == plans[1]
+
+
 def test_command_line_surface():
     """Option names, defaults and choices of the reference's `quantize` command (cli.py:130-300)."""
     from distributed_gptq_b200 import cli
