@@ -649,6 +649,11 @@ def cpu_reference_outright(workload: str, variant: str):
 # ============================================================================= main
 EXCHANGE_NAMES = {"owner": "reduce to owner", "all_reduce": "all_reduce",
                   "peer": "summed by the Hessian kernels in the owner's buffer (peer reductions)"}
+# Size of the CPU sample (1.0 = 3-4 s of timed work on 16 cores): the one-off cpu_baseline of
+# the default run times 10-20 s; every step of the reference arm half of that, so that its
+# warm-up + steps stay within a few minutes.
+CPU_BASELINE_SCALE = 4.0
+REF_ARM_SCALE = 2.0
 E2E_BUDGET_S = 150.0      # time the host-input pass may take (see main)
 
 
@@ -717,7 +722,7 @@ def main():
             if args.cpu_outright and is_model:
                 t, cores, sample = cpu_reference_outright(args.workload, variant)
             else:
-                t, cores, sample = cpu_reference_sample(args.workload, variant)
+                t, cores, sample = cpu_reference_sample(args.workload, variant, REF_ARM_SCALE)
             if i >= args.warmup:
                 times.append(t)
         v = sum(times) / len(times)
@@ -899,7 +904,7 @@ def main():
             }
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            v, cores, sample = cpu_reference_sample(args.workload, variant)
+            v, cores, sample = cpu_reference_sample(args.workload, variant, CPU_BASELINE_SCALE)
             cpu = {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample}
         if is_model:
             config = {"workload": wl.describe(),

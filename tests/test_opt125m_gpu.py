@@ -102,7 +102,9 @@ def test_opt125m_architecture_end_to_end(dgq):
             lvl = (codes.float() - z_gpu[:, gi]) - (r32["codes"].float() - r32["zero"][:, gi])
             assert float((lvl.abs() > 1).float().mean()) <= 5e-4, n
         else:
-            ratio = (1 - m64) / max(1 - o64, 5e-4)
+            # the fp32 oracle's own distance from the fp64 one is 0.1-1 % here and moves from
+            # run to run with the last bits of the Hessian (atomic accumulation order): floored
+            ratio = (1 - m64) / max(1 - o64, 2e-3)
             worst["ratio"] = max(worst["ratio"], ratio)
             assert ratio <= 12.0, (n, m64, o64)
             assert m32 >= 0.94, (n, m32)
