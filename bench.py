@@ -566,6 +566,7 @@ def cpu_reference_sample(workload: str, variant: str, scale: float = 1.0):
     g = torch.Generator().manual_seed(0)
     tok = {Kn: max(2048, int(49152 * scale * (4096 / Kn) ** 2) // 2048 * 2048),
            Kw: max(2048, int(6144 * scale * (11008 / Kw) ** 2) // 2048 * 2048)}
+    tok = {K: min(n, max(2048, T // 2048 * 2048)) for K, n in tok.items()}    # never more than the workload has
     X = {K: torch.randn(tok[K], K, generator=g) for K in (Kn, Kw)}
     rows = max(16, int(512 * scale))
     Wrows = torch.randn(rows, Kn, generator=g) * 0.02
