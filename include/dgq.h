@@ -82,6 +82,10 @@ int32_t dgq_hessian_accum(const void* X_bf16, int64_t T, int32_t K, int64_t ldx,
  * accumulates many batches (core/gptq.py:63-89 is called once per calibration batch) can
  * skip the mirrored half of every update - half of the kernel's reduction traffic - and call
  * dgq_hessian_mirror once, before the matrix is read as a whole (core/gptq.py:112-122).
+ * H is only ever the target of fp32 reductions (nothing is loaded from it), so it may be the
+ * memory of another GPU mapped into this process: ranks that all pass the buffer of the rank
+ * that will quantize the layer have summed their partial Hessians (the all_reduce of
+ * distributed/coordinator.py:224) when their launches have completed.
  */
 int32_t dgq_hessian_accum_upper(const void* X_bf16, int64_t T, int32_t K, int64_t ldx,
                                 float* H, int64_t ldh, float alpha, int32_t splits,
