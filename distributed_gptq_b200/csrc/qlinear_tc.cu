@@ -72,12 +72,19 @@ template <> struct Cvt<__half> {
   static constexpr uint32_t FMT = tc05::FMT_F16;
   static constexpr uint32_t MAGIC = 0x64006400u;
   static constexpr float BASE = 1024.f;
+  static constexpr float MAX_ZERO = 64.f;      // largest |zero| the short conversion is exact for
   static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
   }
+  // the scale as a pair of T, and what T cannot hold of it (nothing: the scale is fp16)
+  static __device__ __forceinline__ void scale_pairs(float sc, uint32_t& hi2, uint32_t& lo2) {
+    hi2 = pack2(sc, sc);
+    lo2 = 0u;
+  }
   // (BASE + c) - (BASE + zero) is exact, the scale is an fp16 number: one rounding
-  static __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint32_t sub, uint32_t mul, float) {
+  static __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint32_t sub, uint32_t mul,
+                                                          uint32_t) {
     const __half2 r = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&v),
                                       *reinterpret_cast<const __half2*>(&sub)),
                               *reinterpret_cast<const __half2*>(&mul));
@@ -88,17 +95,29 @@ template <> struct Cvt<__nv_bfloat16> {
   static constexpr uint32_t FMT = tc05::FMT_BF16;
   static constexpr uint32_t MAGIC = 0x43004300u;
   static constexpr float BASE = 128.f;
+  static constexpr float MAX_ZERO = 16.f;      // |d| <= 31: 5 bits, times the 3 bits of lo = 8
   static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
   }
-  // (BASE + c) - (BASE + zero) is exact in bf16, but the fp16 scale is not a bf16 number: the
-  // difference is widened to fp32 (a shift), multiplied there and rounded once
-  static __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint32_t sub, uint32_t, float sc) {
+  // The fp16 scale (11 significant bits) is not a bf16 number (8): it is split into
+  // hi = bf16(scale) and lo = scale - hi, which has at most 3 significant bits and is a bf16
+  // number too.
+  static __device__ __forceinline__ void scale_pairs(float sc, uint32_t& hi2, uint32_t& lo2) {
+    const float hi = __bfloat162float(__float2bfloat16_rn(sc));
+    hi2 = pack2(hi, hi);
+    lo2 = pack2(sc - hi, sc - hi);
+  }
+  // d = (BASE + c) - (BASE + zero) is exact and at most 5 bits wide (|zero| <= MAX_ZERO), so
+  // d * lo is exact in bf16 and fma(d, hi, d * lo) is the exact product d * scale rounded
+  // once - the value rounding (c - zero) * scale computed in fp32 gives.
+  static __device__ __forceinline__ uint32_t dequant_pair(uint32_t v, uint32_t sub, uint32_t mul,
+                                                          uint32_t mul_lo) {
     const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v),
                                      *reinterpret_cast<const __nv_bfloat162*>(&sub));
-    const uint32_t u = *reinterpret_cast<const uint32_t*>(&d);
-    return pack2(__uint_as_float(u << 16) * sc, __uint_as_float(u & 0xFFFF0000u) * sc);
+    const __nv_bfloat162 t = __hmul2(d, *reinterpret_cast<const __nv_bfloat162*>(&mul_lo));
+    const __nv_bfloat162 r = __hfma2(d, *reinterpret_cast<const __nv_bfloat162*>(&mul), t);
+    return *reinterpret_cast<const uint32_t*>(&r);
   }
 };
 
@@ -233,7 +252,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
       // needed at once would stall the warp for longer than a slice takes
       __half s_next = srow[0], z_next = zrow[0];
       float sc = 0.f, zs = 0.f;
-      uint32_t sub2 = 0u, mul2 = 0u;       // (BASE + zero, BASE + zero) and (scale, scale) as pairs of T
+      uint32_t sub2 = 0u, mul2 = 0u, mul_lo2 = 0u;   // (BASE + zero) x 2, scale x 2 (and its rest) as pairs of T
       bool short_path = false;
       // one slice: this thread's 16 bytes of codes -> 32 values -> four 16-byte pieces of row f
       auto step = [&](int sl, const uint4& codes) -> bool {
@@ -246,9 +265,9 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
           if (g + 1 < a.n_groups) { s_next = srow[g + 1]; z_next = zrow[g + 1]; }
           zs = z * sc;                                       // w = code * scale - zero * scale
           // integer zero points (every GPTQ zero is one) take the short path
-          short_path = (z == rintf(z)) && fabsf(z) <= 64.f;
+          short_path = (z == rintf(z)) && fabsf(z) <= Cvt<T>::MAX_ZERO;
           sub2 = Cvt<T>::pack2(Cvt<T>::BASE + z, Cvt<T>::BASE + z);
-          mul2 = Cvt<T>::pack2(sc, sc);
+          Cvt<T>::scale_pairs(sc, mul2, mul_lo2);
         }
         const bool got = tc05::mbar_wait_bounded(&ctl->empty[s], ph ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
@@ -269,7 +288,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
             for (int b = 0; b < 4; ++b) {
               // byte b of w (low nibble = even column) and of w >> 4 (low nibble = odd column)
               const uint32_t pr = __byte_perm(w, w4, ((4 + b) << 8) | b);
-              o[b] = Cvt<T>::dequant_pair((pr & 0x000F000Fu) | Cvt<T>::MAGIC, sub2, mul2, sc);
+              o[b] = Cvt<T>::dequant_pair((pr & 0x000F000Fu) | Cvt<T>::MAGIC, sub2, mul2, mul_lo2);
             }
           } else {
 #pragma unroll

@@ -62,6 +62,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--beta", type=float, default=0.0, help="gemm: C = A B^T + beta C")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"], help="qlinear: activation type")
     ap.add_argument("--upper", action="store_true",
                     help="hessian: update only the part on and above the diagonal")
     a = ap.parse_args()
@@ -147,16 +148,17 @@ def main():
         ng = K // 128
         s = torch.rand(N, ng, generator=g, device=dev).half() * 0.01
         z = torch.randint(0, 16, (N, ng), generator=g, device=dev).half()
-        x = torch.randn(a.M, K, generator=g, device=dev).to(torch.bfloat16)
+        tdt, cdt = (torch.bfloat16, _C.BF16) if a.dtype == "bf16" else (torch.float16, _C.F16)
+        x = torch.randn(a.M, K, generator=g, device=dev).to(tdt)
         import ctypes
         P = lambda t: ctypes.c_void_p(t.data_ptr())
-        y = torch.empty((a.M, N), dtype=torch.bfloat16, device=dev)
+        y = torch.empty((a.M, N), dtype=tdt, device=dev)
         L = _C.lib()
-        call = lambda: L.dgq_qlinear_forward(P(x), _C.BF16, a.M, P(qw), P(s), P(z), None, None, 0, N, K,
+        call = lambda: L.dgq_qlinear_forward(P(x), cdt, a.M, P(qw), P(s), P(z), None, None, 0, N, K,
                                              ng, 4, 128, P(y), None)
         for t in _time_raw(call, a.reps):
             nbytes = N * K / 2 + 4 * N * ng + 2 * a.M * (K + N)
-            print(f"qlinear M={a.M} N={N} K={K}: {t * 1e3:.1f} us  {nbytes / t / 1e6:.1f} GB/s  "
+            print(f"qlinear {a.dtype} M={a.M} N={N} K={K}: {t * 1e3:.1f} us  {nbytes / t / 1e6:.1f} GB/s  "
                   f"{2.0 * a.M * N * K / t / 1e9:.1f} TFLOP/s")
 
 
