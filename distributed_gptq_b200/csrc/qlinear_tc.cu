@@ -9,11 +9,11 @@
 // 256 rows (two sub-tiles that share the converted weights) and walks K in slices of 64
 // columns; per slice
 //   - warp 0 fetches the slice of x with one TMA box (128-byte swizzle): operand A;
-//   - warps 2-9 ("converters", two threads per output feature) read the feature's 32 bytes of
-//     packed codes straight from global memory (16 bytes per thread, four slices ahead: a load
-//     takes longer than a slice), turn them into 64 values (code - zero) * scale of the
-//     activation type and store them as the feature's 128-byte row of operand B, in the same
-//     swizzled layout a TMA box would have produced;
+//   - warps 2-9 ("converters", two groups of four warps that take alternate slices, one thread
+//     per output feature) read the feature's 32 bytes of packed codes straight from global
+//     memory (two own slices ahead: a load takes longer than a slice), turn them into 64
+//     values (code - zero) * scale of the activation type and store them as the feature's
+//     128-byte row of operand B, in the same swizzled layout a TMA box would have produced;
 //   - warp 1 issues four tcgen05.mma kind::f16 (M = 128 rows, N = 128 features, K = 16) per
 //     sub-tile into that sub-tile's 128-column fp32 accumulator in tensor memory;
 // and warps 10-13 drain finished accumulators (two alternate), add the bias, round and store.
@@ -145,7 +145,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       tc05::mbar_init(&ctl->full[s], 1);
-      tc05::mbar_init(&ctl->conv[s], CONV_WARPS);
+      tc05::mbar_init(&ctl->conv[s], CONV_WARPS / 2);      // the four warps of one group
       tc05::mbar_init(&ctl->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -231,43 +231,64 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
     __syncwarp();
   } else if (warp < 2 + CONV_WARPS) {
     // ------------------------------------------------------------------ converters (weights)
+    // Two groups of four warps take alternate slices (group = parity of the running slice
+    // count), one thread per feature row: a slice's conversion is a chain of dependent steps
+    // (wait for the stage, convert, store, proxy fence, arrive) whose latency, not its
+    // instruction count, bounds a group; two slices in flight hide half of it.
     const int ct = threadIdx.x - 64;                 // 0..255
     const int f = ct & (TILE_N - 1);                 // feature row of the tile
-    const int half = ct >> 7;                        // which 16 of the slice's 32 bytes of codes
+    const int grp = ct >> 7;                         // which slices: (running count + grp) even
     const int slices_per_group = a.n_groups == 1 ? p.n_slices : a.group_size / BK;
-    uint32_t it = 0;
+    uint32_t it0 = 0;                                // slices of the tiles before this one
     bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, it0 += p.n_slices) {
       const int tn = t / p.tiles_m;
       const int n = min(tn * TILE_N + f, a.N_out - 1);       // rows past the end repeat the last
-      const uint8_t* wrow = a.qw + (int64_t)n * a.row_bytes + half * 16;
+      const uint8_t* wrow = a.qw + (int64_t)n * a.row_bytes;
       const __half* srow = a.scales + (int64_t)n * a.n_groups;
       const __half* zrow = a.zeros + (int64_t)n * a.n_groups;
-      auto fetch = [&](int sl) -> uint4 {
-        return sl < p.n_slices ? *reinterpret_cast<const uint4*>(wrow + (int64_t)sl * 32)
-                               : make_uint4(0u, 0u, 0u, 0u);
+      struct Codes { uint4 lo, hi; };                 // the slice's 32 bytes of this row
+      auto fetch = [&](int sl) -> Codes {
+        Codes c;
+        if (sl < p.n_slices) {
+          const uint4* src = reinterpret_cast<const uint4*>(wrow + (int64_t)sl * 32);
+          c.lo = src[0];
+          c.hi = src[1];
+        } else {
+          c.lo = c.hi = make_uint4(0u, 0u, 0u, 0u);
+        }
+        return c;
       };
-      uint4 q0 = fetch(0), q1 = fetch(1), q2 = fetch(2), q3 = fetch(3);
-      // scale and zero of the next group are fetched a group ahead as well: a load that is
-      // needed at once would stall the warp for longer than a slice takes
-      __half s_next = srow[0], z_next = zrow[0];
+      const int first = (int)((it0 + (uint32_t)grp) & 1u);   // this group's first slice of the tile
+      Codes qa = fetch(first), qb = fetch(first + 2);
+      // scale and zero of the group of the next own slice are fetched a slice ahead as well: a
+      // load that is needed at once would stall the warp for longer than a slice takes
+      int cur_g = -1, pre_g = -1;
+      __half s_pre = __float2half(0.f), z_pre = __float2half(0.f);
       float sc = 0.f, zs = 0.f;
       uint32_t sub2 = 0u, mul2 = 0u, mul_lo2 = 0u;   // (BASE + zero) x 2, scale x 2 (and its rest) as pairs of T
       bool short_path = false;
-      // one slice: this thread's 16 bytes of codes -> 32 values -> four 16-byte pieces of row f
-      auto step = [&](int sl, const uint4& codes) -> bool {
+      // one slice: the row's 32 bytes of codes -> 64 values -> the eight 16-byte pieces of row f
+      auto step = [&](int sl, const Codes& codes) -> bool {
+        const uint32_t it = it0 + (uint32_t)sl;
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        ++it;
-        if (sl % slices_per_group == 0) {
-          const int g = sl / slices_per_group;
-          sc = __half2float(s_next);
-          const float z = __half2float(z_next);
-          if (g + 1 < a.n_groups) { s_next = srow[g + 1]; z_next = zrow[g + 1]; }
+        const int g = a.n_groups == 1 ? 0 : sl / slices_per_group;
+        if (g != cur_g) {
+          const __half sv = g == pre_g ? s_pre : srow[g], zv = g == pre_g ? z_pre : zrow[g];
+          cur_g = g;
+          sc = __half2float(sv);
+          const float z = __half2float(zv);
           zs = z * sc;                                       // w = code * scale - zero * scale
           // integer zero points (every GPTQ zero is one) take the short path
           short_path = (z == rintf(z)) && fabsf(z) <= Cvt<T>::MAX_ZERO;
           sub2 = Cvt<T>::pack2(Cvt<T>::BASE + z, Cvt<T>::BASE + z);
           Cvt<T>::scale_pairs(sc, mul2, mul_lo2);
+        }
+        const int gn = a.n_groups == 1 ? 0 : min((sl + 2) / slices_per_group, a.n_groups - 1);
+        if (gn != cur_g && gn != pre_g) {
+          s_pre = srow[gn];
+          z_pre = zrow[gn];
+          pre_g = gn;
         }
         const bool got = tc05::mbar_wait_bounded(&ctl->empty[s], ph ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
@@ -276,11 +297,12 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
         }
         // row f of operand B: eight 16-byte pieces, piece c stored at position c ^ (f % 8)
         uint4* brow = reinterpret_cast<uint4*>(stages + (size_t)s * STAGE_BYTES + A_BYTES) + f * 8;
-        const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+        const uint32_t words[8] = {codes.lo.x, codes.lo.y, codes.lo.z, codes.lo.w,
+                                   codes.hi.x, codes.hi.y, codes.hi.z, codes.hi.w};
         const bool fast = __all_sync(0xffffffffu, short_path);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          // one 32-bit word = 4 bytes = 8 codes = columns 8 (4 half + c) .. + 7 of the slice
+        for (int c = 0; c < 8; ++c) {
+          // one 32-bit word = 4 bytes = 8 codes = columns 8 c .. 8 c + 7 of the slice
           const uint32_t w = words[c], w4 = w >> 4;
           uint32_t o[4];
           if (fast) {
@@ -297,7 +319,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
               o[b] = Cvt<T>::pack2(fmaf(lo, sc, -zs), fmaf(hi, sc, -zs));
             }
           }
-          brow[(4 * half + c) ^ (f & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
+          brow[c ^ (f & 7)] = make_uint4(o[0], o[1], o[2], o[3]);
         }
         // make the generic-proxy writes visible to the tensor core's (async proxy) reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -305,14 +327,12 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
         if (lane == 0) tc05::mbar_arrive(&ctl->conv[s]);
         return true;
       };
-      for (int s_ = 0; s_ < p.n_slices && ok; s_ += 4) {
-        // four slices per turn so that the four code registers have fixed names; each is
-        // refilled, for the slice four ahead, as soon as it has been used
-        ok = step(s_, q0);
-        q0 = fetch(s_ + 4);
-        if (ok && s_ + 1 < p.n_slices) { ok = step(s_ + 1, q1); q1 = fetch(s_ + 5); }
-        if (ok && s_ + 2 < p.n_slices) { ok = step(s_ + 2, q2); q2 = fetch(s_ + 6); }
-        if (ok && s_ + 3 < p.n_slices) { ok = step(s_ + 3, q3); q3 = fetch(s_ + 7); }
+      for (int s_ = first; s_ < p.n_slices && ok; s_ += 4) {
+        // two own slices per turn so that the code registers have fixed names; each is
+        // refilled, for the own slice after the next, as soon as it has been used
+        ok = step(s_, qa);
+        qa = fetch(s_ + 4);
+        if (ok && s_ + 2 < p.n_slices) { ok = step(s_ + 2, qb); qb = fetch(s_ + 6); }
       }
     }
   } else {
