@@ -5,9 +5,9 @@
 // 4-bit codes, two per byte with the even column in the low nibble (the QuantizedLinear
 // layout, models/layers.py:76-93), one fp16 scale/zero per output feature and group of
 // `group_size` consecutive columns (a multiple of 64).  The weights never exist in 16-bit
-// form in global memory: a CTA works on a tile of y of 128 features x 128 rows (M <= 128) or
-// 256 rows (two sub-tiles that share the converted weights) and walks K in slices of 64
-// columns; per slice
+// form in global memory: a CTA works on a tile of y of 128 features x 128 rows (M <= 128),
+// 128 features x 256 rows (two sub-tiles that share the converted weights) or, when there are
+// enough tiles, 256 features x 256 rows, and walks K in slices of 64 columns; per slice
 //   - warp 0 fetches the slice of x with one TMA box (128-byte swizzle): operand A;
 //   - warps 2-9 ("converters", two groups of four warps that take alternate slices, one thread
 //     per output feature) read the feature's 32 bytes of packed codes straight from global
@@ -33,22 +33,31 @@
 
 namespace {
 
-constexpr int SUB_M = 128, TILE_N = 128, BK = 64;
-constexpr int SUB_A_BYTES = SUB_M * BK * 2, B_BYTES = TILE_N * BK * 2;  // 16 KB each
+constexpr int SUB_M = 128, SUB_N = 128, BK = 64;
+constexpr int SUB_A_BYTES = SUB_M * BK * 2, SUB_B_BYTES = SUB_N * BK * 2;   // 16 KB each
 constexpr int MAX_STAGES = 6;
 constexpr int CONV_WARPS = 8;
+constexpr int CONV_THREADS = 32 * CONV_WARPS;
 constexpr int THREADS = 32 * (2 + CONV_WARPS + 4);
 
-// A tile of y is MT sub-tiles of 128 rows against the same 128 features: the converted slice
-// of weights (the expensive operand) then serves MT products.  192 KB of stages either way.
-template <int MT> struct Shape {
-  static constexpr int TILE_M = SUB_M * MT;
-  static constexpr int A_BYTES = SUB_A_BYTES * MT;
+// A tile of y is MT sub-tiles of 128 rows against NT sub-tiles of 128 features.  MT = 2: the
+// converted slice of weights (the expensive operand) serves two products.  NT = 2: the slice of
+// activations does - the 256 x 128 tile reads 128 flop worth of activations per byte from L2,
+// which caps it near 740 TFLOP/s at 5.8 TB/s; 256 x 256 halves those bytes, at the price of a
+// single set of accumulators (all 512 columns of tensor memory), i.e. an epilogue the next
+// tile's products wait for.  192 KB of stages in every shape.
+template <int MT, int NT> struct Shape {
+  static constexpr int TILE_M = SUB_M * MT, TILE_N = SUB_N * NT;
+  static constexpr int A_BYTES = SUB_A_BYTES * MT, B_BYTES = SUB_B_BYTES * NT;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = MT == 1 ? 6 : 4;
-  static constexpr uint32_t ACC_COLS = TILE_N * MT;          // one accumulator set
-  static constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // two sets alternate
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;  // 6, 4, 3
+  static constexpr uint32_t ACC_COLS = SUB_N * NT * MT;      // one accumulator set
+  static constexpr int ACC_SETS = ACC_COLS * 2 <= 512 ? 2 : 1;
+  static constexpr uint32_t TMEM_COLS = ACC_SETS * ACC_COLS;
+  // converter threads per slice: one per feature row; the groups take alternate slices
+  static constexpr int GROUPS = CONV_THREADS / TILE_N;
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+  static_assert(STAGES <= MAX_STAGES && STAGES >= 2 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "shape");
 };
 
 struct Control {
@@ -127,12 +136,13 @@ __device__ __forceinline__ float bias_at(const void* b, int dt, int n) {
   return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(b)[n]);
 }
 
-template <typename T, int MT>
+template <typename T, int MT, int NT>
 __global__ void __launch_bounds__(THREADS, 1)
 qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
-  using S = Shape<MT>;
-  constexpr int TILE_M = S::TILE_M, A_BYTES = S::A_BYTES, STAGE_BYTES = S::STAGE_BYTES;
-  constexpr int STAGES = S::STAGES;
+  using S = Shape<MT, NT>;
+  constexpr int TILE_M = S::TILE_M, TILE_N = S::TILE_N, A_BYTES = S::A_BYTES;
+  constexpr int STAGE_BYTES = S::STAGE_BYTES, STAGES = S::STAGES;
+  constexpr int ACC_SETS = S::ACC_SETS, GROUPS = S::GROUPS;
   constexpr uint32_t TMEM_COLS = S::TMEM_COLS, ACC_COLS = S::ACC_COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* stages = reinterpret_cast<uint8_t*>(
@@ -145,7 +155,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       tc05::mbar_init(&ctl->full[s], 1);
-      tc05::mbar_init(&ctl->conv[s], CONV_WARPS / 2);      // the four warps of one group
+      tc05::mbar_init(&ctl->conv[s], CONV_WARPS / GROUPS); // the warps of one group
       tc05::mbar_init(&ctl->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -190,11 +200,13 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // one instruction covers all NT sub-tiles of features: their rows follow each other in
+      // operand B (128 bytes each, 1024 bytes per group of eight)
       constexpr uint32_t idesc = tc05::make_instr_desc(Cvt<T>::FMT, false, false, SUB_M, TILE_N);
       uint32_t it = 0, lt = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++lt) {
-        const uint32_t ab = lt & 1, aph = (lt >> 1) & 1;
+        const uint32_t ab = lt % ACC_SETS, aph = (lt / ACC_SETS) & 1;
         if (!tc05::mbar_wait_bounded(&ctl->tmem_empty[ab], aph ^ 1, abort_flag)) {
           if (a.info) { a.info[0] = DGQ_INFO_WAIT_TIMEOUT; a.info[1] = 22; }
           break;
@@ -218,7 +230,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
             const uint64_t db = tc05::make_smem_desc(b_base + k * 32, 0, 1024);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              // sub-tile mt: rows 128 mt .. of the box, 16 KB further; its own 128 columns
+              // sub-tile mt: rows 128 mt .. of the box, 16 KB further; its own TILE_N columns
               const uint64_t da = tc05::make_smem_desc(a_base + mt * SUB_A_BYTES + k * 32, 0, 1024);
               tc05::umma_bf16(acc + mt * TILE_N, da, db, idesc, (s_ | k) != 0 ? 1u : 0u);
             }
@@ -236,8 +248,8 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
     // (wait for the stage, convert, store, proxy fence, arrive) whose latency, not its
     // instruction count, bounds a group; two slices in flight hide half of it.
     const int ct = threadIdx.x - 64;                 // 0..255
-    const int f = ct & (TILE_N - 1);                 // feature row of the tile
-    const int grp = ct >> 7;                         // which slices: (running count + grp) even
+    const int f = ct % TILE_N;                       // feature row of the tile
+    const int grp = ct / TILE_N;                     // takes the slices whose running count is grp mod GROUPS
     const int slices_per_group = a.n_groups == 1 ? p.n_slices : a.group_size / BK;
     uint32_t it0 = 0;                                // slices of the tiles before this one
     bool ok = true;
@@ -259,8 +271,9 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
         }
         return c;
       };
-      const int first = (int)((it0 + (uint32_t)grp) & 1u);   // this group's first slice of the tile
-      Codes qa = fetch(first), qb = fetch(first + 2);
+      // this group's first slice of the tile: (it0 + first) % GROUPS == grp
+      const int first = (int)(((uint32_t)grp + GROUPS - it0 % GROUPS) % GROUPS);
+      Codes qa = fetch(first), qb = fetch(first + GROUPS);
       // scale and zero of the group of the next own slice are fetched a slice ahead as well: a
       // load that is needed at once would stall the warp for longer than a slice takes
       int cur_g = -1, pre_g = -1;
@@ -284,7 +297,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
           sub2 = Cvt<T>::pack2(Cvt<T>::BASE + z, Cvt<T>::BASE + z);
           Cvt<T>::scale_pairs(sc, mul2, mul_lo2);
         }
-        const int gn = a.n_groups == 1 ? 0 : min((sl + 2) / slices_per_group, a.n_groups - 1);
+        const int gn = a.n_groups == 1 ? 0 : min((sl + GROUPS) / slices_per_group, a.n_groups - 1);
         if (gn != cur_g && gn != pre_g) {
           s_pre = srow[gn];
           z_pre = zrow[gn];
@@ -327,12 +340,12 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
         if (lane == 0) tc05::mbar_arrive(&ctl->conv[s]);
         return true;
       };
-      for (int s_ = first; s_ < p.n_slices && ok; s_ += 4) {
+      for (int s_ = first; s_ < p.n_slices && ok; s_ += 2 * GROUPS) {
         // two own slices per turn so that the code registers have fixed names; each is
         // refilled, for the own slice after the next, as soon as it has been used
         ok = step(s_, qa);
-        qa = fetch(s_ + 4);
-        if (ok && s_ + 2 < p.n_slices) { ok = step(s_ + 2, qb); qb = fetch(s_ + 6); }
+        qa = fetch(s_ + 2 * GROUPS);
+        if (ok && s_ + GROUPS < p.n_slices) { ok = step(s_ + GROUPS, qb); qb = fetch(s_ + 3 * GROUPS); }
       }
     }
   } else {
@@ -342,7 +355,7 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
     T* y = reinterpret_cast<T*>(a.y);
     for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++lt) {
       const int tm = t % p.tiles_m, tn = t / p.tiles_m;
-      const uint32_t ab = lt & 1, aph = (lt >> 1) & 1;
+      const uint32_t ab = lt % ACC_SETS, aph = (lt / ACC_SETS) & 1;
       const bool got = tc05::mbar_wait_bounded(&ctl->tmem_full[ab], aph, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0 && a.info) { a.info[0] = DGQ_INFO_WAIT_TIMEOUT; a.info[1] = 25; }
@@ -418,9 +431,9 @@ bool qlinear_tc_supported(const QLinearTcArgs& a) {
 
 namespace {
 
-template <int MT>
+template <int MT, int NT>
 bool launch_shape(const QLinearTcArgs& a, cudaStream_t st) {
-  using S = Shape<MT>;
+  using S = Shape<MT, NT>;
   CUtensorMap map_x;
   const CUtensorMapDataType dt = a.dtype == DGQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -430,37 +443,44 @@ bool launch_shape(const QLinearTcArgs& a, cudaStream_t st) {
   Params p;
   p.a = a;
   p.tiles_m = (int)dgq_cdiv(a.M, S::TILE_M);
-  p.tiles_n = (int)dgq_cdiv(a.N_out, TILE_N);
+  p.tiles_n = (int)dgq_cdiv(a.N_out, S::TILE_N);
   p.n_tiles = p.tiles_m * p.tiles_n;
   p.n_slices = a.K / BK;
   const unsigned grid = (unsigned)std::min(p.n_tiles, dgq_sm_count());
   if (a.dtype == DGQ_F16)
-    qlinear_tc_kernel<__half, MT><<<grid, THREADS, S::SMEM_BYTES, st>>>(map_x, p);
+    qlinear_tc_kernel<__half, MT, NT><<<grid, THREADS, S::SMEM_BYTES, st>>>(map_x, p);
   else
-    qlinear_tc_kernel<__nv_bfloat16, MT><<<grid, THREADS, S::SMEM_BYTES, st>>>(map_x, p);
+    qlinear_tc_kernel<__nv_bfloat16, MT, NT><<<grid, THREADS, S::SMEM_BYTES, st>>>(map_x, p);
   dgq_note_launches(1);
   return cudaGetLastError() == cudaSuccess;
 }
 
-template <typename K>
-bool set_smem(K kernel, size_t bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) ==
-         cudaSuccess;
+template <int MT, int NT>
+bool set_smem() {
+  const cudaFuncAttribute at = cudaFuncAttributeMaxDynamicSharedMemorySize;
+  const int bytes = (int)Shape<MT, NT>::SMEM_BYTES;
+  return cudaFuncSetAttribute(qlinear_tc_kernel<__half, MT, NT>, at, bytes) == cudaSuccess &&
+         cudaFuncSetAttribute(qlinear_tc_kernel<__nv_bfloat16, MT, NT>, at, bytes) == cudaSuccess;
 }
 
 }  // namespace
 
 bool qlinear_tc_launch(const QLinearTcArgs& a, cudaStream_t st) {
   static DgqDeviceOnce once;
-  if (!once.run([] {
-        return set_smem(qlinear_tc_kernel<__half, 1>, Shape<1>::SMEM_BYTES) &&
-               set_smem(qlinear_tc_kernel<__nv_bfloat16, 1>, Shape<1>::SMEM_BYTES) &&
-               set_smem(qlinear_tc_kernel<__half, 2>, Shape<2>::SMEM_BYTES) &&
-               set_smem(qlinear_tc_kernel<__nv_bfloat16, 2>, Shape<2>::SMEM_BYTES);
-      }))
+  if (!once.run([] { return set_smem<1, 1>() && set_smem<2, 1>() && set_smem<2, 2>(); }))
     return false;
-  // above one sub-tile of rows the 256-row tile halves the conversions per product
-  return a.M > SUB_M ? launch_shape<2>(a, st) : launch_shape<1>(a, st);
+  if (a.M <= SUB_M) return launch_shape<1, 1>(a, st);
+  // Above one sub-tile of rows the 256-row tile halves the conversions per product, and the
+  // 256-feature tile halves the activation bytes per product too (measured 853 against 740
+  // TFLOP/s with every SM busy) - but a persistent grid's last round is partly idle, and
+  // with few tiles the larger tile loses more to that than it gains.
+  const int64_t sms = dgq_sm_count();
+  auto busy = [&](int64_t tiles) { return (double)tiles / (double)(dgq_cdiv(tiles, sms) * sms); };
+  const int64_t tiles_m = dgq_cdiv(a.M, 2 * SUB_M);
+  const double wide = busy(tiles_m * dgq_cdiv(a.N_out, 2 * SUB_N));
+  const double narrow = busy(tiles_m * dgq_cdiv(a.N_out, SUB_N));
+  if (wide * 853.0 > narrow * 740.0) return launch_shape<2, 2>(a, st);
+  return launch_shape<2, 1>(a, st);
 }
 
 }  // namespace dgq

@@ -131,6 +131,37 @@ def test_qlinear_many_rows(dgq, M, N_out, K, g, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("g", [128, 64])
+def test_qlinear_prefill_sized(dgq, dtype, g):
+    """Enough 256 x 256 tiles for several rounds on every SM: the kernel takes its largest
+    tile (one set of accumulators, one converter group), with ragged edges in both
+    directions.  Checked on a sample of rows (rows are independent)."""
+    M, N_out, K = 4100, 9608, 512
+    assert -(-M // 256) * -(-N_out // 256) >= 4 * torch.cuda.get_device_properties(0).multi_processor_count
+    gen = torch.Generator().manual_seed(11)
+    codes = torch.randint(0, 16, (N_out, K), generator=gen).to(torch.uint8)
+    ng = O.n_groups(K, g)
+    scales = (torch.rand(N_out, ng, generator=gen) * 0.02 + 0.001).half()
+    zeros = torch.randint(0, 16, (N_out, ng), generator=gen).half()
+    bias = torch.randn(N_out, generator=gen).to(dtype)
+    x = torch.randn(M, K, generator=gen).to(dtype)
+    n0 = dgq.launch_count()
+    got = dgq.qlinear_forward(x.cuda(), O.pack_f2(codes, 4).cuda(), scales.cuda(), zeros.cuda(), None,
+                              bias.cuda(), K, 4, g)
+    assert dgq.launch_count() == n0 + 1 and tuple(got.shape) == (M, N_out)
+    rows = torch.cat([torch.arange(0, 8), torch.randint(0, M, (240,), generator=gen),
+                      torch.arange(M - 8, M)])
+    Wt = O.dequant(codes, scales, zeros, None, g).to(dtype).double()
+    exact = x[rows].double() @ Wt.t() + bias.double()
+    out_eps = {torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8}[dtype]
+    err = (got[rows.cuda()].double().cpu() - exact).abs().max()
+    assert float(err) <= 1.01 * out_eps * float(exact.abs().max()) + 1e-6
+    # the other rows: finite, and consistent with the sampled ones in magnitude
+    assert bool(torch.isfinite(got).all())
+    assert float(got.float().abs().max()) <= 1.5 * float(exact.abs().max()) + 1.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_qlinear_many_rows_fractional_zero_points(dgq, dtype):
     """Zero points that are not integers (the flat round-to-nearest helpers produce them) take the
     kernel's fp32 dequantization instead of the two-instruction one."""
