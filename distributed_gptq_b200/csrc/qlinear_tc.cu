@@ -9,14 +9,16 @@
 // 128 features x 256 rows (two sub-tiles that share the converted weights) or, when there are
 // enough tiles, 256 features x 256 rows, and walks K in slices of 64 columns; per slice
 //   - warp 0 fetches the slice of x with one TMA box (128-byte swizzle): operand A;
-//   - warps 2-9 ("converters", two groups of four warps that take alternate slices, one thread
-//     per output feature) read the feature's 32 bytes of packed codes straight from global
+//   - warps 2-17 ("converters", one thread per output feature and slice; with 128 features per
+//     tile four groups of four warps, with 256 two groups of eight, each group taking every
+//     fourth / second slice) read the feature's 32 bytes of packed codes straight from global
 //     memory (two own slices ahead: a load takes longer than a slice), turn them into 64
 //     values (code - zero) * scale of the activation type and store them as the feature's
 //     128-byte row of operand B, in the same swizzled layout a TMA box would have produced;
 //   - warp 1 issues four tcgen05.mma kind::f16 (M = 128 rows, N = 128 features, K = 16) per
 //     sub-tile into that sub-tile's 128-column fp32 accumulator in tensor memory;
-// and warps 10-13 drain finished accumulators (two alternate), add the bias, round and store.
+// and warps 18-21 drain finished accumulators (two sets alternate where they fit), add the
+// bias, round and store.
 // CTAs are persistent; tiles are ordered with the row tile running fastest, so the CTAs
 // running at one time share packed weights through L2.
 //
@@ -36,15 +38,15 @@ namespace {
 constexpr int SUB_M = 128, SUB_N = 128, BK = 64;
 constexpr int SUB_A_BYTES = SUB_M * BK * 2, SUB_B_BYTES = SUB_N * BK * 2;   // 16 KB each
 constexpr int MAX_STAGES = 6;
-constexpr int CONV_WARPS = 8;
+constexpr int CONV_WARPS = 16;
 constexpr int CONV_THREADS = 32 * CONV_WARPS;
 constexpr int THREADS = 32 * (2 + CONV_WARPS + 4);
 
 // A tile of y is MT sub-tiles of 128 rows against NT sub-tiles of 128 features.  MT = 2: the
 // converted slice of weights (the expensive operand) serves two products.  NT = 2: the slice of
-// activations does - the 256 x 128 tile reads 128 flop worth of activations per byte from L2,
-// which caps it near 740 TFLOP/s at 5.8 TB/s; 256 x 256 halves those bytes, at the price of a
-// single set of accumulators (all 512 columns of tensor memory), i.e. an epilogue the next
+// activations does, and one product instruction covers 256 features (with the conversion left
+// out, the 256 x 128 pipeline runs at 1.0 PFLOP/s, the 256 x 256 one at 1.4-1.5), at the price
+// of a single set of accumulators (all 512 columns of tensor memory), i.e. an epilogue the next
 // tile's products wait for.  192 KB of stages in every shape.
 template <int MT, int NT> struct Shape {
   static constexpr int TILE_M = SUB_M * MT, TILE_N = SUB_N * NT;
@@ -243,11 +245,12 @@ qlinear_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
     __syncwarp();
   } else if (warp < 2 + CONV_WARPS) {
     // ------------------------------------------------------------------ converters (weights)
-    // Two groups of four warps take alternate slices (group = parity of the running slice
-    // count), one thread per feature row: a slice's conversion is a chain of dependent steps
-    // (wait for the stage, convert, store, proxy fence, arrive) whose latency, not its
-    // instruction count, bounds a group; two slices in flight hide half of it.
-    const int ct = threadIdx.x - 64;                 // 0..255
+    // GROUPS groups of converter warps take every GROUPS-th slice (group = running slice count
+    // mod GROUPS), one thread per feature row: a slice's conversion is a chain of dependent
+    // steps (wait for the stage, convert, store, proxy fence, arrive) whose latency, not its
+    // instruction count, bounds a group (with the conversion left out the same pipeline runs
+    // at 1.4-1.5 PFLOP/s); several slices in flight hide part of it.
+    const int ct = threadIdx.x - 64;                 // 0..CONV_THREADS-1
     const int f = ct % TILE_N;                       // feature row of the tile
     const int grp = ct / TILE_N;                     // takes the slices whose running count is grp mod GROUPS
     const int slices_per_group = a.n_groups == 1 ? p.n_slices : a.group_size / BK;
@@ -471,7 +474,7 @@ bool qlinear_tc_launch(const QLinearTcArgs& a, cudaStream_t st) {
     return false;
   if (a.M <= SUB_M) return launch_shape<1, 1>(a, st);
   // Above one sub-tile of rows the 256-row tile halves the conversions per product, and the
-  // 256-feature tile halves the activation bytes per product too (measured 853 against 740
+  // 256-feature tile halves the activation bytes per product too (measured 1090 against 910
   // TFLOP/s with every SM busy) - but a persistent grid's last round is partly idle, and
   // with few tiles the larger tile loses more to that than it gains.
   const int64_t sms = dgq_sm_count();
@@ -479,7 +482,7 @@ bool qlinear_tc_launch(const QLinearTcArgs& a, cudaStream_t st) {
   const int64_t tiles_m = dgq_cdiv(a.M, 2 * SUB_M);
   const double wide = busy(tiles_m * dgq_cdiv(a.N_out, 2 * SUB_N));
   const double narrow = busy(tiles_m * dgq_cdiv(a.N_out, SUB_N));
-  if (wide * 853.0 > narrow * 740.0) return launch_shape<2, 2>(a, st);
+  if (wide * 1090.0 > narrow * 910.0) return launch_shape<2, 2>(a, st);
   return launch_shape<2, 1>(a, st);
 }
 
