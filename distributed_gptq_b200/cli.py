@@ -56,6 +56,10 @@ def create_parser() -> argparse.ArgumentParser:
     q.add_argument("--output-dir", default="./quantized_models")
     q.add_argument("--save-format", default="safetensors", choices=["safetensors", "pytorch"])
     q.add_argument("--checkpoint-dir", help="keep one shard per finished block here and resume from it")
+    q.add_argument("--hessian-exchange", default="owner", choices=["owner", "all_reduce", "peer"],
+                   help="several ranks: reduce each Hessian to the rank that quantizes the layer "
+                        "(default), all_reduce it like the reference, or let every rank's Hessian "
+                        "kernel accumulate into the owner's buffer over NVLink")
     q.add_argument("--include-lm-head", action="store_true",
                    help="also quantize linear layers outside the decoder blocks")
     q.add_argument("--seed", type=int, default=0)
@@ -156,6 +160,7 @@ def quantize_command(args) -> None:
     from . import DistributedGPTQuantizer, QuantizationConfig
     from .coordinator import create_distributed_config
     dcfg = create_distributed_config()
+    dcfg.hessian_exchange = args.hessian_exchange
     model, tok = load_model(args.model, _dtype(args.torch_dtype))
     vocab = getattr(model.config, "vocab_size", 32000)
     ids = calibration_ids(args, vocab, tok)

@@ -296,6 +296,7 @@ def test_command_line_surface():
     assert (a.bits, a.group_size, a.damp, a.num_samples, a.seq_len, a.batch_size, a.dataset,
             a.torch_dtype, a.output_dir, a.act_order, a.true_sequential) == \
         (4, 128, 0.01, 128, 2048, 1, "wikitext", "float16", "./quantized_models", False, False)
+    assert a.hessian_exchange == "owner"        # not in the reference: how partial Hessians are summed
     import pytest
     with pytest.raises(SystemExit):
         cli.create_parser().parse_args(["quantize", "--model", "m", "--bits", "5"])
