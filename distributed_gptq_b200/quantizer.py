@@ -27,7 +27,6 @@ from __future__ import annotations
 import inspect
 import json
 import logging
-import os
 import time
 from dataclasses import asdict, dataclass
 from pathlib import Path
@@ -37,7 +36,7 @@ import torch
 import torch.nn as nn
 
 from . import _C, io, peer
-from .coordinator import (DistributedConfig, DistributedGPTQCoordinator, assign_owners,
+from .coordinator import (DistributedConfig, DistributedGPTQCoordinator,
                           create_distributed_config, layer_cost)
 from .gptq import GPTQ, quantize_group_launch
 from .streams import ChainPool
